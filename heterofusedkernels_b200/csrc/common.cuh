@@ -1,0 +1,212 @@
+// Shared device-side primitives of the KV-cache data path: 16-byte streaming
+// loads/stores, the bulk-copy (TMA, untiled) PTX wrappers with bounded waits,
+// and the per-device status word that kernels raise instead of faulting.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/hfk_b200.h"
+
+namespace hfk {
+
+// Per-device status word.  Kernels OR bits into it (HFK_DEV_*) when they skip
+// work because an id is out of range or a bounded wait ran out; the host reads
+// and clears it through hfk_device_status().
+__device__ unsigned int g_status_word;
+
+__device__ __forceinline__ void raise_status(unsigned int bit) { atomicOr(&g_status_word, bit); }
+
+// ---- 16-byte streaming accesses ------------------------------------------
+// Every byte on this path is touched exactly once, so both sides use the
+// evict-first (.cs) policy and never allocate in L1.
+__device__ __forceinline__ uint4 ld_stream16(const uint4 *p) {
+  uint4 v;
+  asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream16(uint4 *p, const uint4 &v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+// Whole-CTA copy of n16 16-byte vectors.  Each thread keeps kUnroll independent
+// loads in flight before the first store; a warp touches 512 contiguous bytes
+// per instruction, so every PCIe/HBM transaction is a full, aligned line.
+template <int kThreads, int kUnroll>
+__device__ __forceinline__ void cta_copy16(uint4 *__restrict__ dst, const uint4 *__restrict__ src,
+                                           int64_t n16) {
+  const int tid = threadIdx.x;
+  int64_t base = 0;
+  for (; base + (int64_t)kThreads * kUnroll <= n16; base += (int64_t)kThreads * kUnroll) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) v[u] = ld_stream16(src + base + u * kThreads + tid);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) st_stream16(dst + base + u * kThreads + tid, v[u]);
+  }
+  for (int64_t i = base + tid; i < n16; i += kThreads) st_stream16(dst + i, ld_stream16(src + i));
+}
+
+// ---- mbarrier + bulk copy (cp.async.bulk, untiled) -----------------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase with the given parity, for at most kWaitLimitNs.  Returns
+// false when it gave up; the caller raises HFK_DEV_WAIT_TIMEOUT and leaves.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+  }
+  return true;
+}
+// global -> this CTA's shared memory, completion counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes,
+                                          uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_addr(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(smem_addr(bar))
+      : "memory");
+}
+// this CTA's shared memory -> global, tracked by the thread's bulk group.
+__device__ __forceinline__ void bulk_store(void *gdst, const void *smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
+               "r"(smem_addr(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- the descriptor pump --------------------------------------------------
+// One warp per CTA.  All 32 lanes compute copy descriptors (source, destination,
+// byte count) 32 at a time; lane 0 then drives a ring of kStages shared-memory
+// stages: bulk load into a stage, wait on the stage's mbarrier, bulk store out
+// of it, and reuse the stage once the store has finished reading it.  No data
+// passes through registers and 31 of the 32 lanes only do address arithmetic,
+// so the kernel leaves the SM's issue slots and register file to whatever
+// compute kernel shares the SM.
+struct CopyDesc {
+  const void *src;
+  void *dst;
+  uint32_t bytes;  // 0 = nothing to do (skipped unit)
+};
+
+constexpr int kPumpLag = 2;  // stores allowed to be still reading shared memory
+
+struct PumpSmem {
+  uint64_t full[32];      // one mbarrier per stage (kStages <= 32)
+  CopyDesc desc[64];      // two batches of 32 descriptors
+};
+
+// make_desc(k) returns the descriptor of this CTA's k-th unit, k < total.
+template <typename MakeDesc>
+__device__ __forceinline__ void run_pump(PumpSmem *ps, unsigned char *stages, int stage_bytes,
+                                         int n_stages, int64_t total, uint32_t &seq,
+                                         MakeDesc make_desc) {
+  const int lane = threadIdx.x & 31;
+  const int in_flight = n_stages - kPumpLag;  // loads kept in flight
+  int64_t issued = 0, done = 0;
+  bool ok = true;
+  auto fill_batch = [&](int64_t first) {
+    const int64_t k = first + lane;
+    CopyDesc d;
+    d.src = nullptr; d.dst = nullptr; d.bytes = 0;
+    if (k < total) d = make_desc(k);
+    ps->desc[(first & 32) + lane] = d;
+    __syncwarp();
+  };
+  auto issue_load = [&](int64_t k) {
+    const CopyDesc d = ps->desc[k & 63];
+    const uint32_t q = seq + (uint32_t)k;
+    const int slot = q % n_stages;
+    if (lane == 0) {
+      if (d.bytes != 0) {
+        mbar_expect_tx(&ps->full[slot], d.bytes);
+        bulk_load(stages + (size_t)slot * stage_bytes, d.src, d.bytes, &ps->full[slot]);
+      } else {
+        mbar_arrive(&ps->full[slot]);  // a skipped unit still completes its phase
+      }
+    }
+  };
+  while (done < total && ok) {
+    while (issued < total && issued < done + in_flight) {
+      if ((issued & 31) == 0) fill_batch(issued);
+      if (issued >= n_stages) {
+        // stage reuse: the store of unit (issued - n_stages) must have read its stage
+        if (lane == 0) bulk_wait_read<kPumpLag>();
+      }
+      issue_load(issued);
+      ++issued;
+    }
+    const CopyDesc d = ps->desc[done & 63];
+    const uint32_t q = seq + (uint32_t)done;
+    const int slot = q % n_stages;
+    const uint32_t parity = (q / n_stages) & 1u;
+    if (d.bytes != 0) {
+      if (lane == 0) {
+        ok = mbar_wait_bounded(&ps->full[slot], parity);
+        if (ok) {
+          fence_async_proxy();
+          bulk_store(d.dst, stages + (size_t)slot * stage_bytes, d.bytes);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+    }
+    if (lane == 0) bulk_commit();  // one group per unit, empty for skipped units
+    ++done;
+  }
+  if (!ok && lane == 0) raise_status(HFK_DEV_WAIT_TIMEOUT);
+  if (lane == 0) bulk_wait_all();
+  seq += (uint32_t)total;
+  __syncwarp();
+}
+
+}  // namespace hfk

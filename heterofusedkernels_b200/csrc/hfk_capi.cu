@@ -1,0 +1,452 @@
+// C ABI of libhfk_b200.so: argument validation, launch planning and kernel
+// launches.  The reference's counterpart is its host op layer
+// (pcieThrough/csrc/host/gather_torch.cpp:30-54,
+//  pcieThrough/csrc/host/multi_layer_block_transfer_torch.cpp:58-106) together
+// with the tiling planner (pcieThrough/csrc/host/tiling/multi_layer_block_transfer.cpp:19-56);
+// on CUDA the plan travels as kernel parameters, so nothing is uploaded per call.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "block_transfer.cuh"
+#include "common.cuh"
+#include "host_util.h"
+#include "kv_swap.cuh"
+#include "paged_gather.cuh"
+#include "row_gather.cuh"
+
+namespace hfk {
+
+thread_local std::string t_last_error;
+
+int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  t_last_error = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+  return fail(HFK_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+// ---- tuning state ----------------------------------------------------------
+std::atomic<int> g_stage_bytes{0}, g_n_stages{0}, g_vec_threads{0}, g_vec_unroll{0};
+
+constexpr int kDefaultStageBytes = 32768;
+constexpr int kDefaultStages = 6;
+constexpr int kMaxDynSmem = 227 * 1024;
+constexpr int kSmCount = 148;
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct BulkPlan {
+  int stage_bytes, n_stages;
+  size_t smem;
+};
+// Ring geometry of the bulk mover for a copy unit of `unit_bytes`, leaving
+// `tables_bytes` of shared memory for the id / prefix tables.
+static BulkPlan plan_bulk(int64_t unit_bytes, size_t tables_bytes) {
+  BulkPlan p;
+  p.stage_bytes = g_stage_bytes.load() > 0 ? g_stage_bytes.load() : kDefaultStageBytes;
+  if (unit_bytes < p.stage_bytes) p.stage_bytes = (int)((unit_bytes + 127) / 128 * 128);
+  p.n_stages = g_n_stages.load() > 0 ? g_n_stages.load() : kDefaultStages;
+  const size_t fixed = sizeof(PumpSmem) + tables_bytes + 256;
+  while (p.n_stages > kPumpLag + 1 && (size_t)p.stage_bytes * p.n_stages + fixed > kMaxDynSmem)
+    --p.n_stages;
+  if (p.n_stages > 32) p.n_stages = 32;
+  p.smem = (size_t)p.stage_bytes * p.n_stages + fixed;
+  return p;
+}
+
+template <typename K>
+static cudaError_t allow_smem(K kernel, size_t bytes) {
+  if (bytes <= 48 * 1024) return cudaSuccess;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+// ---- swap ------------------------------------------------------------------
+static int validate_swap(const hfk_swap_desc *d) {
+  if (!d) return fail(HFK_ERR_INVALID_ARG, "swap: descriptor is null");
+  if (!d->k_layer_ptrs || !d->v_layer_ptrs || !d->host_pool)
+    return fail(HFK_ERR_INVALID_ARG, "swap: null pointer table or host pool");
+  if (d->n_blocks < 0 || d->layers <= 0)
+    return fail(HFK_ERR_INVALID_ARG, "swap: n_blocks=%lld layers=%d", (long long)d->n_blocks,
+                d->layers);
+  if (d->n_blocks > 0 && (!d->device_block_ids || !d->host_slot_ids))
+    return fail(HFK_ERR_INVALID_ARG, "swap: null id list");
+  if (d->block_bytes <= 0 || d->num_device_blocks <= 0 || d->num_host_slots <= 0)
+    return fail(HFK_ERR_INVALID_ARG, "swap: block_bytes, num_device_blocks and num_host_slots must be positive");
+  if (d->device_block_stride < d->block_bytes)
+    return fail(HFK_ERR_INVALID_ARG, "swap: device_block_stride %lld < block_bytes %lld",
+                (long long)d->device_block_stride, (long long)d->block_bytes);
+  if ((d->block_bytes | d->device_block_stride | d->host_slot_stride | d->host_layer_stride |
+       d->host_kv_stride) & 15)
+    return fail(HFK_ERR_ALIGNMENT, "swap: block_bytes and all strides must be multiples of 16 bytes");
+  if (!aligned16(d->host_pool)) return fail(HFK_ERR_ALIGNMENT, "swap: host pool is not 16-byte aligned");
+  if (d->layers > 4096) return fail(HFK_ERR_TOO_LARGE, "swap: more than 4096 layers");
+  return HFK_OK;
+}
+
+static SwapArgs to_args(const hfk_swap_desc *d) {
+  SwapArgs a;
+  a.k_layer_ptrs = d->k_layer_ptrs;
+  a.v_layer_ptrs = d->v_layer_ptrs;
+  a.host_pool = static_cast<unsigned char *>(d->host_pool);
+  a.device_block_ids = d->device_block_ids;
+  a.host_slot_ids = d->host_slot_ids;
+  a.ids_are_int64 = d->ids_are_int64;
+  a.layers = d->layers;
+  a.n_blocks = d->n_blocks;
+  a.block_bytes = d->block_bytes;
+  a.device_block_stride = d->device_block_stride;
+  a.host_slot_stride = d->host_slot_stride;
+  a.host_layer_stride = d->host_layer_stride;
+  a.host_kv_stride = d->host_kv_stride;
+  a.num_device_blocks = d->num_device_blocks;
+  a.num_host_slots = d->num_host_slots;
+  return a;
+}
+
+template <bool kToHost, int kThreads, int kUnroll>
+static cudaError_t launch_swap_vector(const SwapArgs &a, int ctas, size_t smem, cudaStream_t s) {
+  auto k = kv_swap_vector_kernel<kToHost, kThreads, kUnroll>;
+  cudaError_t e = allow_smem(k, smem);
+  if (e != cudaSuccess) return e;
+  k<<<ctas, kThreads, smem, s>>>(a);
+  return cudaGetLastError();
+}
+
+template <bool kToHost>
+static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t stream) {
+  int rc = validate_swap(d);
+  if (rc != HFK_OK) return rc;
+  if (d->n_blocks == 0) return HFK_OK;
+  const SwapArgs a = to_args(d);
+  const size_t tables = sizeof(SwapTables) + 2 * sizeof(void *) * (size_t)d->layers;
+  if (mover == HFK_MOVER_AUTO) mover = kToHost ? kDefaultMoverOut : kDefaultMoverIn;
+  const int64_t items = d->n_blocks * 2 * d->layers;
+  if (mover == HFK_MOVER_VECTOR) {
+    if (ctas <= 0) ctas = kDefaultSwapCtasVector;
+    if (ctas > items) ctas = (int)items;
+    const int th = g_vec_threads.load(), un = g_vec_unroll.load();
+    cudaError_t e;
+    if (th == 0 || (th == 512 && un == 4)) e = launch_swap_vector<kToHost, 512, 4>(a, ctas, tables, stream);
+    else if (th == 256 && un == 8) e = launch_swap_vector<kToHost, 256, 8>(a, ctas, tables, stream);
+    else if (th == 256 && un == 4) e = launch_swap_vector<kToHost, 256, 4>(a, ctas, tables, stream);
+    else if (th == 1024 && un == 2) e = launch_swap_vector<kToHost, 1024, 2>(a, ctas, tables, stream);
+    else if (th == 128 && un == 8) e = launch_swap_vector<kToHost, 128, 8>(a, ctas, tables, stream);
+    else return fail(HFK_ERR_UNSUPPORTED, "swap: vector geometry %dx%d is not compiled", th, un);
+    if (e != cudaSuccess) return cuda_fail(e, "kv_swap_vector_kernel launch");
+    return HFK_OK;
+  }
+  if (mover == HFK_MOVER_BULK) {
+    const BulkPlan p = plan_bulk(d->block_bytes, tables);
+    if (ctas <= 0) ctas = kDefaultSwapCtasBulk;
+    const int64_t pieces = (d->block_bytes + p.stage_bytes - 1) / p.stage_bytes;
+    if (ctas > items * pieces) ctas = (int)(items * pieces);
+    auto k = kv_swap_bulk_kernel<kToHost>;
+    cudaError_t e = allow_smem(k, p.smem);
+    if (e != cudaSuccess) return cuda_fail(e, "kv_swap_bulk_kernel attribute");
+    k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "kv_swap_bulk_kernel launch");
+    return HFK_OK;
+  }
+  return fail(HFK_ERR_INVALID_ARG, "swap: unknown mover %d", mover);
+}
+
+// ---- paged gather ----------------------------------------------------------
+static int validate_gather(const hfk_paged_gather_desc *d) {
+  if (!d) return fail(HFK_ERR_INVALID_ARG, "paged_gather: descriptor is null");
+  if (!d->k_layer_ptrs || !d->v_layer_ptrs || !d->k_out || !d->v_out)
+    return fail(HFK_ERR_INVALID_ARG, "paged_gather: null pointer table or output");
+  if (d->layers <= 0 || d->num_seqs < 0 || d->block_size <= 0 || d->token_bytes <= 0 ||
+      d->max_blocks_per_seq < 0 || d->num_device_blocks <= 0 || d->total_tokens < 0)
+    return fail(HFK_ERR_INVALID_ARG, "paged_gather: non-positive geometry");
+  if (d->num_seqs > HFK_MAX_SEQS)
+    return fail(HFK_ERR_TOO_LARGE, "paged_gather: %lld sequences > HFK_MAX_SEQS=%d",
+                (long long)d->num_seqs, HFK_MAX_SEQS);
+  if (d->num_seqs > 0 && (!d->block_tables || !d->seq_lens))
+    return fail(HFK_ERR_INVALID_ARG, "paged_gather: null block table or sequence lengths");
+  if (d->block_table_stride < d->max_blocks_per_seq)
+    return fail(HFK_ERR_INVALID_ARG, "paged_gather: block_table_stride < max_blocks_per_seq");
+  if (d->device_block_stride < d->block_size * d->token_bytes)
+    return fail(HFK_ERR_INVALID_ARG, "paged_gather: device_block_stride smaller than one block");
+  if ((d->token_bytes | d->device_block_stride | d->out_layer_stride) & 15)
+    return fail(HFK_ERR_ALIGNMENT, "paged_gather: token_bytes and strides must be multiples of 16 bytes");
+  if (!aligned16(d->k_out) || !aligned16(d->v_out))
+    return fail(HFK_ERR_ALIGNMENT, "paged_gather: outputs are not 16-byte aligned");
+  if (d->num_seqs * d->max_blocks_per_seq >= (int64_t)1 << 31)
+    return fail(HFK_ERR_TOO_LARGE, "paged_gather: more than 2^31 pages");
+  if (d->layers > 1 && d->out_layer_stride < d->total_tokens * d->token_bytes)
+    return fail(HFK_ERR_INVALID_ARG, "paged_gather: out_layer_stride smaller than one layer's output");
+  return HFK_OK;
+}
+
+template <int kThreads, int kUnroll>
+static cudaError_t launch_gather_vector(const GatherArgs &a, int ctas, cudaStream_t s) {
+  auto k = paged_gather_vector_kernel<kThreads, kUnroll>;
+  const size_t smem = sizeof(GatherTables);
+  cudaError_t e = allow_smem(k, smem);
+  if (e != cudaSuccess) return e;
+  k<<<ctas, kThreads, smem, s>>>(a);
+  return cudaGetLastError();
+}
+
+static int gather_impl(const hfk_paged_gather_desc *d, int mover, int ctas, cudaStream_t stream) {
+  int rc = validate_gather(d);
+  if (rc != HFK_OK) return rc;
+  if (d->num_seqs == 0 || d->max_blocks_per_seq == 0) return HFK_OK;
+  GatherArgs a;
+  a.k_layer_ptrs = d->k_layer_ptrs;
+  a.v_layer_ptrs = d->v_layer_ptrs;
+  a.k_out = static_cast<unsigned char *>(d->k_out);
+  a.v_out = static_cast<unsigned char *>(d->v_out);
+  a.out_layer_stride = d->out_layer_stride;
+  a.block_tables = d->block_tables;
+  a.seq_lens = d->seq_lens;
+  a.ids_are_int64 = d->ids_are_int64;
+  a.layers = d->layers;
+  a.num_seqs = (int)d->num_seqs;
+  a.max_blocks_per_seq = d->max_blocks_per_seq;
+  a.block_table_stride = d->block_table_stride;
+  a.block_size = d->block_size;
+  a.token_bytes = d->token_bytes;
+  a.device_block_stride = d->device_block_stride;
+  a.num_device_blocks = d->num_device_blocks;
+  a.total_tokens = d->total_tokens;
+  if (mover == HFK_MOVER_AUTO) mover = kDefaultMoverGather;
+  if (mover == HFK_MOVER_VECTOR) {
+    if (ctas <= 0) ctas = kDefaultGatherCtasVector;
+    const int th = g_vec_threads.load(), un = g_vec_unroll.load();
+    cudaError_t e;
+    if (th == 0 || (th == 256 && un == 8)) e = launch_gather_vector<256, 8>(a, ctas, stream);
+    else if (th == 512 && un == 4) e = launch_gather_vector<512, 4>(a, ctas, stream);
+    else if (th == 256 && un == 4) e = launch_gather_vector<256, 4>(a, ctas, stream);
+    else if (th == 1024 && un == 2) e = launch_gather_vector<1024, 2>(a, ctas, stream);
+    else if (th == 128 && un == 8) e = launch_gather_vector<128, 8>(a, ctas, stream);
+    else return fail(HFK_ERR_UNSUPPORTED, "paged_gather: vector geometry %dx%d is not compiled", th, un);
+    if (e != cudaSuccess) return cuda_fail(e, "paged_gather_vector_kernel launch");
+    return HFK_OK;
+  }
+  if (mover == HFK_MOVER_BULK) {
+    const BulkPlan p = plan_bulk(d->block_size * d->token_bytes, sizeof(GatherTables));
+    if (ctas <= 0) ctas = kDefaultGatherCtasBulk;
+    auto k = paged_gather_bulk_kernel;
+    cudaError_t e = allow_smem(k, p.smem);
+    if (e != cudaSuccess) return cuda_fail(e, "paged_gather_bulk_kernel attribute");
+    k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "paged_gather_bulk_kernel launch");
+    return HFK_OK;
+  }
+  return fail(HFK_ERR_INVALID_ARG, "paged_gather: unknown mover %d", mover);
+}
+
+// ---- Group R ---------------------------------------------------------------
+static int row_gather_impl(const void *table, void *dst, const void *ids, int ids64, size_t num_ids,
+                           size_t row_bytes, size_t num_rows, int ctas, cudaStream_t stream) {
+  if (!table || !dst || (!ids && num_ids))
+    return fail(HFK_ERR_INVALID_ARG, "gather: null table, destination or id list");
+  if (row_bytes == 0) return fail(HFK_ERR_INVALID_ARG, "gather: row_bytes is 0");
+  if (num_ids == 0) return HFK_OK;
+  if (ctas <= 0) ctas = kDefaultRowGatherCtas;
+  // the reference clamps the core count to the number of ids (gather_torch.cpp:48)
+  if ((size_t)ctas > num_ids) ctas = (int)num_ids;
+  RowGatherArgs a;
+  a.table = static_cast<const unsigned char *>(table);
+  a.dst = static_cast<unsigned char *>(dst);
+  a.ids = ids;
+  a.ids_are_int64 = ids64;
+  a.num_ids = (int64_t)num_ids;
+  a.row_bytes = (int64_t)row_bytes;
+  a.num_rows = (int64_t)num_rows;
+  const bool vec = (row_bytes & 15) == 0 && aligned16(table) && aligned16(dst);
+  if (vec && row_bytes <= 1024) {
+    row_gather_small_kernel<256><<<ctas, 256, 0, stream>>>(a);
+  } else if (vec) {
+    row_gather_large_kernel<512, 4><<<ctas, 512, 0, stream>>>(a);
+  } else if ((row_bytes & 3) == 0 && ((uintptr_t)table & 3) == 0 && ((uintptr_t)dst & 3) == 0) {
+    row_gather_words_kernel<256, uint32_t><<<ctas, 256, 0, stream>>>(a);
+  } else {
+    row_gather_words_kernel<256, unsigned char><<<ctas, 256, 0, stream>>>(a);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "row gather launch");
+  return HFK_OK;
+}
+
+static int transfer_impl(void *const *layer_ptrs, const void *src, int64_t B, int64_t L, int64_t H,
+                         int64_t D, int64_t elt, int ctas, cudaStream_t stream) {
+  if (!layer_ptrs || !src)
+    return fail(HFK_ERR_INVALID_ARG, "multi_layer_block_transfer: null pointer table or source block");
+  if (B <= 0 || L <= 0 || H <= 0 || D <= 0 || elt <= 0)
+    return fail(HFK_ERR_INVALID_ARG, "multi_layer_block_transfer: non-positive geometry");
+  if ((D * elt) & 15)
+    return fail(HFK_ERR_ALIGNMENT,
+                "multi_layer_block_transfer: head_dim*elt_size=%lld is not a multiple of 16 bytes",
+                (long long)(D * elt));
+  if (!aligned16(src)) return fail(HFK_ERR_ALIGNMENT, "multi_layer_block_transfer: source is not 16-byte aligned");
+  if (L > 4096) return fail(HFK_ERR_TOO_LARGE, "multi_layer_block_transfer: more than 4096 layers");
+  TransferArgs a;
+  a.layer_ptrs = layer_ptrs;
+  a.src = static_cast<const unsigned char *>(src);
+  a.block_size = B;
+  a.layers = L;
+  a.heads = H;
+  a.d16 = D * elt / 16;
+  if (ctas <= 0) ctas = kDefaultTransferCtas;
+  const int64_t total = B * L * H * a.d16;
+  const int64_t max_ctas = (total + 511) / 512;
+  if (ctas > max_ctas) ctas = (int)max_ctas;
+  block_transfer_kernel<512, 4><<<ctas, 512, (size_t)L * sizeof(void *), stream>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "block_transfer_kernel launch");
+  return HFK_OK;
+}
+
+}  // namespace hfk
+
+using namespace hfk;
+
+extern "C" {
+
+const char *hfk_strerror(int code) {
+  switch (code) {
+    case HFK_OK: return "ok";
+    case HFK_ERR_INVALID_ARG: return "invalid argument";
+    case HFK_ERR_ALIGNMENT: return "address or size is not a multiple of 16 bytes";
+    case HFK_ERR_NOT_REGISTERED: return "host pointer is not inside a registered range";
+    case HFK_ERR_CUDA: return "CUDA runtime error";
+    case HFK_ERR_TOO_LARGE: return "size beyond the supported maximum";
+    case HFK_ERR_NO_MEMORY: return "host allocation or registration failed";
+    case HFK_ERR_UNSUPPORTED: return "unsupported combination";
+    default: return "unknown error";
+  }
+}
+
+const char *hfk_last_error_message(void) { return t_last_error.c_str(); }
+const char *hfk_version(void) { return "0.1.0"; }
+
+int hfk_device_status(unsigned int *status_bits, hfk_stream_t stream) {
+  if (!status_bits) return fail(HFK_ERR_INVALID_ARG, "device_status: null output");
+  cudaError_t e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+  unsigned int v = 0;
+  e = cudaMemcpyFromSymbol(&v, g_status_word, sizeof(v));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyFromSymbol(status)");
+  if (v != 0) {
+    const unsigned int zero = 0;
+    e = cudaMemcpyToSymbol(g_status_word, &zero, sizeof(zero));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyToSymbol(status)");
+  }
+  *status_bits = v;
+  return HFK_OK;
+}
+
+int hfk_set_bulk_geometry(int stage_bytes, int n_stages) {
+  if (stage_bytes < 0 || n_stages < 0 || (stage_bytes & 127) || n_stages > 32 ||
+      (n_stages > 0 && n_stages <= kPumpLag))
+    return fail(HFK_ERR_INVALID_ARG, "bulk geometry: stage_bytes %% 128 == 0, %d < n_stages <= 32",
+                kPumpLag);
+  if ((size_t)stage_bytes * (n_stages > 0 ? n_stages : kPumpLag + 1) > (size_t)kMaxDynSmem - 20480)
+    return fail(HFK_ERR_TOO_LARGE, "bulk geometry: ring does not fit shared memory");
+  g_stage_bytes = stage_bytes;
+  g_n_stages = n_stages;
+  return HFK_OK;
+}
+
+int hfk_set_vector_geometry(int threads, int unroll) {
+  g_vec_threads = threads;
+  g_vec_unroll = unroll;
+  return HFK_OK;
+}
+
+int hfk_swap_out(const hfk_swap_desc *desc, int mover, int ctas, hfk_stream_t stream) {
+  return swap_impl<true>(desc, mover, ctas, stream);
+}
+int hfk_swap_in(const hfk_swap_desc *desc, int mover, int ctas, hfk_stream_t stream) {
+  return swap_impl<false>(desc, mover, ctas, stream);
+}
+
+int hfk_swap_copy_engine(const hfk_swap_desc *d, int to_host, hfk_stream_t stream) {
+  int rc = validate_swap(d);
+  if (rc != HFK_OK) return rc;
+  // Every array of the descriptor is a host array here: the addresses are
+  // formed on the CPU and each chunk becomes one copy-engine transfer.
+  for (int64_t i = 0; i < d->n_blocks; ++i) {
+    const int64_t dev = d->ids_are_int64 ? static_cast<const int64_t *>(d->device_block_ids)[i]
+                                         : static_cast<const int32_t *>(d->device_block_ids)[i];
+    const int64_t slot = d->ids_are_int64 ? static_cast<const int64_t *>(d->host_slot_ids)[i]
+                                          : static_cast<const int32_t *>(d->host_slot_ids)[i];
+    if (dev < 0 || dev >= d->num_device_blocks)
+      return fail(HFK_ERR_INVALID_ARG, "swap_copy_engine: device block id %lld out of range at %lld",
+                  (long long)dev, (long long)i);
+    if (slot < 0 || slot >= d->num_host_slots)
+      return fail(HFK_ERR_INVALID_ARG, "swap_copy_engine: host slot id %lld out of range at %lld",
+                  (long long)slot, (long long)i);
+  }
+  for (int64_t i = 0; i < d->n_blocks; ++i) {
+    const int64_t dev = d->ids_are_int64 ? static_cast<const int64_t *>(d->device_block_ids)[i]
+                                         : static_cast<const int32_t *>(d->device_block_ids)[i];
+    const int64_t slot = d->ids_are_int64 ? static_cast<const int64_t *>(d->host_slot_ids)[i]
+                                          : static_cast<const int32_t *>(d->host_slot_ids)[i];
+    for (int l = 0; l < d->layers; ++l) {
+      for (int kv = 0; kv < 2; ++kv) {
+        unsigned char *dp = static_cast<unsigned char *>(kv ? d->v_layer_ptrs[l] : d->k_layer_ptrs[l]) +
+                            dev * d->device_block_stride;
+        unsigned char *hp = static_cast<unsigned char *>(d->host_pool) + slot * d->host_slot_stride +
+                            (int64_t)l * d->host_layer_stride + kv * d->host_kv_stride;
+        cudaError_t e = to_host ? cudaMemcpyAsync(hp, dp, (size_t)d->block_bytes, cudaMemcpyDeviceToHost, stream)
+                                : cudaMemcpyAsync(dp, hp, (size_t)d->block_bytes, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(chunk)");
+      }
+    }
+  }
+  return HFK_OK;
+}
+
+int hfk_paged_gather(const hfk_paged_gather_desc *desc, int mover, int ctas, hfk_stream_t stream) {
+  return gather_impl(desc, mover, ctas, stream);
+}
+
+int hfk_gather(const void *table, void *dst, const void *ids, int ids_are_int64, size_t num_ids,
+               size_t row_bytes, size_t num_rows, int ctas, hfk_stream_t stream) {
+  return row_gather_impl(table, dst, ids, ids_are_int64, num_ids, row_bytes, num_rows, ctas, stream);
+}
+
+int hfk_multi_layer_block_transfer(void *const *device_layer_ptrs, const void *src_block,
+                                   int64_t block_size, int64_t layers, int64_t heads,
+                                   int64_t head_dim, int64_t elt_size, int ctas,
+                                   hfk_stream_t stream) {
+  return transfer_impl(device_layer_ptrs, src_block, block_size, layers, heads, head_dim, elt_size,
+                       ctas, stream);
+}
+
+int hfk_fused_memcpy_multi_layer_block_transfer(void *const *device_layer_ptrs,
+                                                const void *host_block, void *staging,
+                                                int64_t block_size, int64_t layers, int64_t heads,
+                                                int64_t head_dim, int64_t elt_size, int ctas,
+                                                hfk_stream_t stream) {
+  if (!host_block || !staging)
+    return fail(HFK_ERR_INVALID_ARG, "fused_memcpy_multi_layer_block_transfer: null host block or staging");
+  if (block_size <= 0 || layers <= 0 || heads <= 0 || head_dim <= 0 || elt_size <= 0)
+    return fail(HFK_ERR_INVALID_ARG, "fused_memcpy_multi_layer_block_transfer: non-positive geometry");
+  const size_t bytes = (size_t)block_size * layers * heads * head_dim * elt_size;
+  // stage 1 on the copy engine (multi_layer_block_transfer_torch.cpp:97-100) ...
+  cudaError_t e = cudaMemcpyAsync(staging, host_block, bytes, cudaMemcpyHostToDevice, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(staging)");
+  // ... stage 2: the same kernel, reading the staging buffer (:105)
+  return transfer_impl(device_layer_ptrs, staging, block_size, layers, heads, head_dim, elt_size,
+                       ctas, stream);
+}
+
+}  // extern "C"

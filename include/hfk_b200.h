@@ -1,0 +1,259 @@
+/*
+ * hfk_b200.h — C ABI of the B200-native KV-cache data path (libhfk_b200.so).
+ *
+ * This is the drop-in boundary: plain pointers and sizes, a CUDA stream handle
+ * and an int status.  No torch types, no C++ types and no exceptions cross it.
+ * The torch operator library `pcie_through` and the pybind module
+ * `heterofusedkernels.memory` are thin shims over these functions.
+ *
+ * The model for the shape of this ABI is the launch ABI of the reference,
+ *   extern "C" uint32_t aclrtlaunch_<kernel>(uint32_t blockDim, aclrtStream, args...)
+ * (pcieThrough/csrc/include/aclrtlaunch_kernels.h:9-10): a core count, a
+ * stream, raw addresses.  Here `ctas` plays the role of `blockDim`/`aiv`
+ * ("how many cores to spend"): it is the number of CUDA thread blocks that
+ * the persistent kernel is launched with; `ctas <= 0` selects the default of
+ * the entry point.
+ *
+ * Conventions
+ *  - Every compute entry point enqueues work on `stream` and returns without
+ *    synchronising, like the reference's EXEC_KERNEL_CMD
+ *    (pcieThrough/csrc/host/launch_utils.h:26-38).  Unlike the reference it
+ *    checks the launch status and returns it.
+ *  - "device-accessible" means: a device allocation, or the device alias of a
+ *    host range registered through hfk_register_ptr / hfk_alloc_pinned_numa_ptr.
+ *  - Return value: HFK_OK (0) or a negative HFK_ERR_* code;
+ *    hfk_last_error_message() gives the detail for the calling thread.
+ *  - Ids that are out of range are detected ON THE DEVICE: the kernel skips the
+ *    block, sets a bit in a per-device status word and never forms the bad
+ *    address.  hfk_device_status() reads and clears that word.
+ */
+#ifndef HFK_B200_H_
+#define HFK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t without including the CUDA headers. */
+typedef struct CUstream_st *hfk_stream_t;
+
+/* ---- status codes ------------------------------------------------------- */
+#define HFK_OK 0
+#define HFK_ERR_INVALID_ARG (-1)    /* null pointer, non-positive count, bad enum */
+#define HFK_ERR_ALIGNMENT (-2)      /* address or byte count not a multiple of 16 */
+#define HFK_ERR_NOT_REGISTERED (-3) /* host pointer outside every registered range */
+#define HFK_ERR_CUDA (-4)           /* a CUDA runtime call failed */
+#define HFK_ERR_TOO_LARGE (-5)      /* size beyond a stated maximum */
+#define HFK_ERR_NO_MEMORY (-6)      /* mmap / mbind / registration failed */
+#define HFK_ERR_UNSUPPORTED (-7)    /* combination not implemented */
+
+/* bits of the device status word (hfk_device_status) */
+#define HFK_DEV_BAD_DEVICE_BLOCK_ID 0x1u /* device block id outside [0, num_device_blocks) */
+#define HFK_DEV_BAD_HOST_SLOT_ID 0x2u    /* host slot id outside [0, num_host_slots) */
+#define HFK_DEV_BAD_ROW_ID 0x4u          /* gather row id outside [0, num_rows) */
+#define HFK_DEV_BAD_SEQ_LEN 0x8u         /* sequence longer than its block table row */
+#define HFK_DEV_WAIT_TIMEOUT 0x10u       /* a bounded mbarrier wait gave up */
+
+const char *hfk_strerror(int code);
+const char *hfk_last_error_message(void);
+/* Library version, "major.minor.patch". */
+const char *hfk_version(void);
+
+/* Reads the status word of the current device into *status_bits and clears it.
+ * Synchronises `stream` first, so it is not for the hot loop. */
+int hfk_device_status(unsigned int *status_bits, hfk_stream_t stream);
+
+/* Tuning knobs, process-wide, meant for benchmarking.  Ring of the bulk mover:
+ * stage_bytes (multiple of 128) x n_stages of shared memory per CTA; vector
+ * mover: threads per CTA x 16-byte loads in flight per thread (only a few
+ * combinations are compiled).  0 restores the default. */
+int hfk_set_bulk_geometry(int stage_bytes, int n_stages);
+int hfk_set_vector_geometry(int threads, int unroll);
+
+/* ======================================================================== *
+ *  Host-memory registry and NUMA-local pinned allocation
+ * ======================================================================== */
+
+/* Registers [ptr, ptr+size) with the current CUDA device as mapped, portable
+ * pinned memory and records host ptr -> device alias.  Registering a base that
+ * is already recorded returns the existing alias.  Returns the device alias,
+ * NULL on failure.
+ * Replaces register_ptr (common/csrc/managed_memory/managed_mem.cpp:305-323)
+ * and HostRegisteredMemoryManager::registerHostPtr (:45-66). */
+void *hfk_register_ptr(void *ptr, size_t size);
+
+/* Removes the record whose base is `ptr` and unregisters the range.  Unknown
+ * pointers are not an error (returns 0), as in the reference.
+ * Replaces unregister_ptr (managed_mem.cpp:325-334) / aclUnregisterHostPtr (:105-119). */
+int hfk_unregister_ptr(void *ptr);
+
+/* Device alias of a host address that lies inside a registered range, 0 if it
+ * lies in none.  Replaces get_device_ptr (managed_mem.cpp:372-375) and
+ * HostRegisteredMemoryManager::getDevicePtr (:139-160). */
+uintptr_t hfk_get_device_ptr(uintptr_t host_ptr);
+
+/* Size of the registered range that contains `ptr`, 0 if none.
+ * Replaces HostRegisteredMemoryManager::getRecordSize (managed_mem.cpp:163-179). */
+size_t hfk_get_record_size(void *ptr);
+
+/* Number of live records. */
+int hfk_registry_count(void);
+
+/* Unregisters everything (the reference does this in the singleton's
+ * destructor, managed_mem.cpp:26-41). */
+void hfk_unregister_all(void);
+
+/* Test hook: with `on` != 0 the registry stops calling the CUDA driver and
+ * hands out the host address itself as the alias, so that the bookkeeping
+ * (range lookup, duplicates, removal) can be tested on a machine without a
+ * GPU.  No compute entry point consults this switch. */
+void hfk_registry_set_test_driver(int on);
+
+/* NUMA node of CUDA device `device` (-1 = current device), read from
+ * /sys/bus/pci/devices/<bdf>/numa_node; -1 when the platform reports none.
+ * Returns HFK_ERR_* (< -1) on failure.
+ * Replaces the DCMI + sysfs lookup in alloc_numa_pinned_tensor
+ * (common/csrc/mem_alloc.cpp:18-38, common/csrc/dcmi_management.cpp:27-39). */
+int hfk_device_numa_node(int device);
+
+/* PCI bus id of CUDA device `device` (-1 = current) as lower-case
+ * "dddd:bb:dd.f" into buf.  Returns HFK_OK or an error. */
+int hfk_device_pci_bus_id(int device, char *buf, size_t buf_len);
+
+/* mmap + mbind(MPOL_BIND) to `node` (skipped when node == -1) + zero fill +
+ * register.  Returns the host address, NULL on failure.
+ * Replaces alloc_pinned_numa_ptr (common/csrc/mem_alloc.cpp:79-115). */
+void *hfk_alloc_pinned_numa_ptr(size_t size, int node);
+
+/* Unregister + munmap of a pointer obtained from hfk_alloc_pinned_numa_ptr.
+ * Replaces free_pinned_numa_ptr (common/csrc/mem_alloc.cpp:66-77). */
+int hfk_free_pinned_numa_ptr(void *ptr);
+
+/* ======================================================================== *
+ *  Group R — operators whose semantics are fixed by the reference
+ * ======================================================================== */
+
+/* dst[i, 0:row_bytes] = table[ids[i], 0:row_bytes] for i < num_ids.
+ * table: device-accessible (host-registered alias or device memory);
+ * dst, ids: device memory.  ids are int64 (ids_are_int64 != 0) or int32.
+ * num_rows > 0 enables the on-device range check of the ids.
+ * Replaces gather_kernel (pcieThrough/csrc/kernel/gather.cpp:7-48,
+ * gather.h:35-134) and its launch (pcieThrough/csrc/host/gather_torch.cpp:53). */
+int hfk_gather(const void *table, void *dst, const void *ids, int ids_are_int64,
+               size_t num_ids, size_t row_bytes, size_t num_rows, int ctas,
+               hfk_stream_t stream);
+
+/* One KV block, all layers, with re-layout:
+ *   for t < block_size, l < layers, h < heads:
+ *     device_layer_ptrs[l][h][t][0:head_dim] = src_block[t][l][h][0:head_dim]
+ * device_layer_ptrs: DEVICE array of `layers` pointers, each to an
+ * [heads, block_size, head_dim] buffer; src_block: device-accessible
+ * [block_size, layers, heads, head_dim].  head_dim*elt_size must be a
+ * multiple of 16 bytes.
+ * Replaces the kernel multi_layer_block_transfer
+ * (pcieThrough/csrc/kernel/multi_layer_block_transfer_kernel.cpp:8-29,
+ * multi_layer_block_transfer_kernel.h:42-82) and its tiling
+ * (pcieThrough/csrc/host/tiling/multi_layer_block_transfer.cpp:19-56). */
+int hfk_multi_layer_block_transfer(void *const *device_layer_ptrs, const void *src_block,
+                                   int64_t block_size, int64_t layers, int64_t heads,
+                                   int64_t head_dim, int64_t elt_size, int ctas,
+                                   hfk_stream_t stream);
+
+/* Staged twin: cudaMemcpyAsync(staging <- host_block) on the copy engine, then
+ * the kernel above reading `staging` (device memory of the same size).
+ * Replaces fused_memcpy_multi_layer_block_transfer
+ * (pcieThrough/csrc/host/multi_layer_block_transfer_torch.cpp:82-106). */
+int hfk_fused_memcpy_multi_layer_block_transfer(void *const *device_layer_ptrs,
+                                                const void *host_block, void *staging,
+                                                int64_t block_size, int64_t layers,
+                                                int64_t heads, int64_t head_dim,
+                                                int64_t elt_size, int ctas,
+                                                hfk_stream_t stream);
+
+/* ======================================================================== *
+ *  Group N — multi-block, all-layer K/V swap and paged gather
+ *  (no counterpart function in the reference; conventions follow
+ *   pcieThrough/README.md:25-27 for pointer tables and
+ *   pcieThrough/csrc/host/gather_torch.cpp:38,44-46 for id tensors)
+ * ======================================================================== */
+
+/* Which data mover a swap uses. */
+#define HFK_MOVER_AUTO 0   /* the entry point's tuned default */
+#define HFK_MOVER_VECTOR 1 /* 16-byte ld/st loops, whole CTA */
+#define HFK_MOVER_BULK 2   /* one thread per CTA pumping cp.async.bulk through shared memory */
+
+typedef struct hfk_swap_desc {
+  /* DEVICE arrays of `layers` pointers: base of layer l's K (resp. V) cache,
+   * laid out [num_device_blocks][block_bytes (+ padding up to device_block_stride)]. */
+  void *const *k_layer_ptrs;
+  void *const *v_layer_ptrs;
+  /* Device alias of the host pool.  Chunk (slot s, layer l, kv) starts at
+   * host_pool + s*host_slot_stride + l*host_layer_stride + kv*host_kv_stride. */
+  void *host_pool;
+  /* DEVICE arrays of n_blocks ids; int64 when ids_are_int64 != 0, else int32. */
+  const void *device_block_ids;
+  const void *host_slot_ids;
+  int ids_are_int64;
+  int layers;
+  int64_t n_blocks;
+  int64_t block_bytes;         /* bytes of one (block, layer, K|V) chunk; multiple of 16 */
+  int64_t device_block_stride; /* bytes between consecutive device blocks (>= block_bytes) */
+  int64_t host_slot_stride;
+  int64_t host_layer_stride;
+  int64_t host_kv_stride;
+  int64_t num_device_blocks;   /* range check of device_block_ids */
+  int64_t num_host_slots;      /* range check of host_slot_ids */
+} hfk_swap_desc;
+
+/* Swap-out: for every i < n_blocks, layer l, kv in {K,V}:
+ *   host chunk(host_slot_ids[i], l, kv) = device chunk(device_block_ids[i], l, kv)
+ * one launch for all layers.  host slots must be distinct. */
+int hfk_swap_out(const hfk_swap_desc *desc, int mover, int ctas, hfk_stream_t stream);
+
+/* Swap-in: the inverse copy; device block ids must be distinct. */
+int hfk_swap_in(const hfk_swap_desc *desc, int mover, int ctas, hfk_stream_t stream);
+
+/* Copy-engine alternative: one cudaMemcpyAsync per chunk.  All five arrays of
+ * the descriptor (pointer tables and id lists) are HOST arrays here, and
+ * host_pool is the HOST address of the pinned pool.  to_host != 0 = swap-out. */
+int hfk_swap_copy_engine(const hfk_swap_desc *desc_with_host_arrays, int to_host,
+                         hfk_stream_t stream);
+
+typedef struct hfk_paged_gather_desc {
+  void *const *k_layer_ptrs; /* DEVICE arrays of `layers` cache bases, as in hfk_swap_desc */
+  void *const *v_layer_ptrs;
+  void *k_out; /* [layers][total_tokens][token_bytes], layer l at k_out + l*out_layer_stride */
+  void *v_out;
+  int64_t out_layer_stride;
+  /* DEVICE int32/int64 array [num_seqs][max_blocks_per_seq] (row stride in elements
+   * = block_table_stride) and DEVICE array [num_seqs] of sequence lengths in tokens. */
+  const void *block_tables;
+  const void *seq_lens;
+  int ids_are_int64;
+  int layers;
+  int64_t num_seqs;           /* <= HFK_MAX_SEQS */
+  int64_t max_blocks_per_seq;
+  int64_t block_table_stride;
+  int64_t block_size;         /* tokens per block */
+  int64_t token_bytes;        /* kv_heads*head_dim*elt_size; multiple of 16 */
+  int64_t device_block_stride;/* bytes between cache blocks (>= block_size*token_bytes) */
+  int64_t num_device_blocks;  /* range check of the table entries */
+  int64_t total_tokens;       /* capacity of k_out/v_out in tokens (range check) */
+} hfk_paged_gather_desc;
+
+#define HFK_MAX_SEQS 1024
+
+/* Paged gather: sequence s owns output tokens [cu(s), cu(s)+seq_lens[s]) where cu
+ * is the exclusive prefix sum of seq_lens; its j-th page is copied from
+ * cache block block_tables[s][j] (the last page partially).  All layers, K and V,
+ * one launch. */
+int hfk_paged_gather(const hfk_paged_gather_desc *desc, int mover, int ctas,
+                     hfk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HFK_B200_H_ */
