@@ -1,0 +1,439 @@
+#!/usr/bin/env python
+"""Benchmark of the KV-cache data path: multi-layer paged-KV swap over PCIe (headline) and the
+paged gather in HBM (secondary, single-GPU runs).
+
+    python bench.py --gpus N --steps K --warmup W          # this implementation
+    python bench.py --impl reference ...                    # the CPU restatement on the host cores
+
+A *step* is one pass of the hot path over one batch: one swap-out call (HBM -> pinned host pool)
+followed by one swap-in call (host pool -> HBM, other device blocks) of the workload's block
+count, all layers, K and V.  Each rank owns its own cache, pool and PCIe link; there is no
+collective on the data path, so scaling is weak (per-GPU work fixed).  torch.distributed is used
+only for the start barrier and the max-over-ranks reduction of the device-side time.
+
+Prints ONE JSON line (rank 0).  `value` is the whole-job GB/s with the id lists resident on the
+device; `e2e` drives the same step through the public API (PagedKVCache.swap_out / swap_in) with
+host-resident id lists and reads the status word back every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+GB = 1e9
+
+
+# --------------------------------------------------------------------------- workloads
+def geometry(name: str):
+    """Shapes of the benchmark configurations (seeded synthetic data stands in for serving traffic)."""
+    from types import SimpleNamespace as NS
+
+    fp8 = getattr(torch, "float8_e4m3fn", torch.uint8)
+    table = {
+        "llama3_8b_swap": NS(layers=32, num_blocks=20000, block_size=16, kv_heads=8, head_dim=128,
+                             dtype=torch.bfloat16, host_slots=40000, n_swap=512),
+        "llama3_70b_tp8_swap": NS(layers=80, num_blocks=6000, block_size=128, kv_heads=1, head_dim=128,
+                                  dtype=torch.bfloat16, host_slots=24000, n_swap=2048),
+        "qwen2_7b_fp8_swap": NS(layers=28, num_blocks=8192, block_size=16, kv_heads=4, head_dim=128,
+                                dtype=fp8, host_slots=16384, n_swap=256),
+        "tiny": NS(layers=2, num_blocks=64, block_size=16, kv_heads=8, head_dim=128, dtype=torch.float16,
+                   host_slots=128, n_swap=8),
+    }
+    g = table[name]
+    g.name = name
+    g.elt = torch.empty((), dtype=g.dtype).element_size()
+    g.block_bytes = g.block_size * g.kv_heads * g.head_dim * g.elt
+    g.swap_bytes = g.n_swap * g.layers * 2 * g.block_bytes
+    return g
+
+
+def mem_available_bytes() -> int:
+    for line in Path("/proc/meminfo").read_text().splitlines():
+        if line.startswith("MemAvailable:"):
+            return int(line.split()[1]) * 1024
+    return 0
+
+
+def fill_random_bytes(t: torch.Tensor, seed: int) -> None:
+    """Cheap seeded fill on the device: random bytes (for fp8 without the NaN codes 0x7F/0xFF)."""
+    gen = torch.Generator(device=t.device).manual_seed(seed)
+    flat = t.view(torch.uint8).view(-1)
+    step = 1 << 30
+    for i in range(0, flat.numel(), step):
+        part = flat[i:i + step]
+        part.copy_(torch.randint(0, 254, part.shape, dtype=torch.uint8, device=t.device, generator=gen))
+        if t.element_size() == 1:
+            part += (part >= 0x7F).to(torch.uint8)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms in the background."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU baseline
+def cpu_baseline_swap(g, steps: int, warmup: int, budget_s: float = 25.0) -> dict:
+    """The torch CPU restatement (index_select / index_copy_ per layer) on the host cores.
+
+    Sample: the full step's bytes (n_swap blocks, every layer, K and V, out then in) on a cache and a
+    pool shrunk to 2*n_swap blocks, so only the pools are smaller, not the bytes moved."""
+    from oracle import kv_oracle as o
+
+    nb = 2 * g.n_swap
+    shape = (nb, g.block_size, g.kv_heads, g.head_dim)
+    store = torch.empty((2, g.layers) + shape[:1] + (g.block_bytes,), dtype=torch.uint8)
+    store.random_(0, 254, generator=torch.Generator().manual_seed(0))
+    dev_k = list(store[0].unbind(0))
+    dev_v = list(store[1].unbind(0))
+    pool = torch.zeros((nb, g.layers, 2, g.block_bytes), dtype=torch.uint8)
+    times = []
+    t_start = time.perf_counter()
+    for s in range(warmup + steps):
+        ids = o.distinct_ids(g.n_swap, nb, 10 + s)
+        slots = o.distinct_ids(g.n_swap, nb, 20 + s)
+        back = o.distinct_ids(g.n_swap, nb, 30 + s)
+        t0 = time.perf_counter()
+        o.swap_out(dev_k, dev_v, pool, ids, slots)
+        o.swap_in(dev_k, dev_v, pool, back, slots)
+        dt = time.perf_counter() - t0
+        if s >= warmup:
+            times.append(dt)
+        if time.perf_counter() - t_start > budget_s and len(times) >= 1:
+            break
+    mean = sum(times) / len(times)
+    return {"value": 2 * g.swap_bytes / mean / GB, "unit": "GB/s", "cores": torch.get_num_threads(),
+            "host_cpus": os.cpu_count(), "kind": "port",
+            "sample": (f"{len(times)} full steps ({g.n_swap} blocks x {g.layers} layers x K,V, out then in = "
+                       f"{2 * g.swap_bytes} bytes each) on a cache and pool shrunk to {nb} blocks; torch CPU "
+                       "index_select/index_copy_ per layer"),
+            "ms_per_step": mean * 1e3, "steps": len(times)}
+
+
+# --------------------------------------------------------------------------- PCIe peak
+def measure_pcie_peak(pool_u8: torch.Tensor, device) -> dict:
+    """Best-of-5 cudaMemcpyAsync of up to 1 GiB between the pinned pool and device memory."""
+    n = min(pool_u8.numel(), 1 << 30)
+    host = pool_u8[:n]
+    dev = torch.empty(n, dtype=torch.uint8, device=device)
+    res = {}
+    for name, dst, src in (("h2d", dev, host), ("d2h", host, dev)):
+        best = 0.0
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            dst.copy_(src, non_blocking=True)
+            b.record()
+            b.synchronize()
+            best = max(best, n / (a.elapsed_time(b) * 1e-3) / GB)
+        res[name] = best
+    res["bytes"] = n
+    res["pinned"] = bool(host.is_pinned())
+    del dev
+    return res
+
+
+# --------------------------------------------------------------------------- gather leg
+def bench_gather(device, steps: int, warmup: int, mover, aiv) -> dict:
+    """Paged gather, Llama-3-8B layout: 64 sequences of 512..8192 tokens (seeded), block tables that are
+    disjoint slices of a seeded permutation of a 40000-block cache, all 32 layers, K and V, one launch."""
+    from heterofusedkernels_b200.connector import PagedKVCache
+    from oracle import kv_oracle as o
+
+    layers, nblocks, bs, heads, hd = 32, 40000, 16, 8, 128
+    lens = o.gather_seq_lens(seed=0)
+    total = sum(lens)
+    token_bytes = heads * hd * 2
+    need = 2 * layers * nblocks * bs * token_bytes + 2 * layers * total * token_bytes
+    free, _ = torch.cuda.mem_get_info(device)
+    note = ""
+    if need > free - (4 << 30):
+        nblocks = max(sum((n + bs - 1) // bs for n in lens) + 1,
+                      int((free - (6 << 30) - 2 * layers * total * token_bytes) // (2 * layers * bs * token_bytes)))
+        note = f"cache shrunk to {nblocks} blocks to fit free HBM"
+    cache = PagedKVCache(layers, nblocks, bs, heads, hd, torch.bfloat16, device)
+    fill_random_bytes(cache._k_store, 1)
+    fill_random_bytes(cache._v_store, 2)
+    tables = o.block_tables_for(lens, bs, nblocks, seed=1).to(device)
+    lens_t = torch.tensor(lens, device=device)
+    k_out = torch.empty((layers, total, heads, hd), dtype=torch.bfloat16, device=device)
+    v_out = torch.empty_like(k_out)
+    algo = 2 * total * token_bytes * 2 * layers  # read + write of K and V outputs
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s in range(warmup + steps):
+        if s >= warmup:
+            ev[s - warmup][0].record()
+        cache.paged_gather(tables, lens_t, k_out, v_out, aiv=aiv, mover=mover)
+        if s >= warmup:
+            ev[s - warmup][1].record()
+    torch.cuda.synchronize()
+    ms = [a.elapsed_time(b) for a, b in ev]
+    status = cache.status()
+    # spot check against torch indexing on the device (layer 3, K, sequence 5)
+    s5 = 5
+    nb5 = (lens[s5] + bs - 1) // bs
+    ref = cache.k_caches[3][tables[s5, :nb5]].flatten(0, 1)[:lens[s5]]
+    start = sum(lens[:s5])
+    ok = torch.equal(ref.view(torch.int16), k_out[3, start:start + lens[s5]].view(torch.int16))
+    mean_ms = sum(ms) / len(ms)
+    res = {"workload": "llama3_8b_gather", "total_tokens": total, "num_seqs": len(lens), "layers": layers,
+           "algorithmic_bytes": algo, "ms_per_launch": mean_ms, "best_ms": min(ms),
+           "value": algo / (mean_ms * 1e-3) / GB, "unit": "GB/s", "status_word": status, "spot_check_ok": bool(ok),
+           "note": note}
+    del cache, k_out, v_out
+    torch.cuda.empty_cache()
+    return res
+
+
+# --------------------------------------------------------------------------- main
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="llama3_8b_swap")
+    ap.add_argument("--mover", default="auto", choices=["auto", "vector", "bulk"])
+    ap.add_argument("--aiv", type=int, default=0, help="CTAs per swap kernel (0 = library default)")
+    ap.add_argument("--gather-aiv", type=int, default=0)
+    ap.add_argument("--host-slots", type=int, default=0, help="override the host pool size (slots)")
+    ap.add_argument("--no-gather", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    g = geometry(args.workload)
+    config = {"workload": g.name, "layers": g.layers, "block_size": g.block_size, "kv_heads": g.kv_heads,
+              "head_dim": g.head_dim, "kv_dtype": str(g.dtype).replace("torch.", ""),
+              "blocks_per_swap": g.n_swap, "device_blocks": g.num_blocks,
+              "bytes_per_direction_per_gpu": g.swap_bytes, "parallelism": f"{world} independent ranks, no collective",
+              "l2": "inputs larger than L2 (each direction moves >= 1 GB of distinct blocks per step)"}
+
+    if args.impl == "reference":
+        # the reference semantics (torch CPU index_select / index_copy_ per layer) on the host cores
+        if rank != 0:
+            return
+        cb = cpu_baseline_swap(g, args.steps, min(args.warmup, 1), budget_s=120.0)
+        line = {"impl": "reference", "metric": "kv_swap_GBps", "value": cb["value"], "unit": "GB/s",
+                "n_gpus": args.gpus, "steps": cb["steps"], "warmup": min(args.warmup, 1),
+                "ms_per_step": cb["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "u8", "data": "synthetic", "config": config, "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
+
+    import heterofusedkernels_b200 as pkg
+    from heterofusedkernels_b200.connector import PagedKVCache
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # noqa: F811
+
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    mover = {"auto": None, "vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK}[args.mover]
+    aiv = args.aiv if args.aiv > 0 else None
+
+    # ---- workload state (outside every timed region) -----------------------------------
+    slot_bytes = g.layers * 2 * g.block_bytes
+    host_slots = args.host_slots or g.host_slots
+    budget = int(mem_available_bytes() * 0.6 / max(world, 1))
+    pool_note = ""
+    if host_slots * slot_bytes > budget:
+        host_slots = max(2 * g.n_swap, budget // slot_bytes)
+        pool_note = f"host pool shrunk to {host_slots} slots (MemAvailable), transferred set unchanged"
+    t0 = time.perf_counter()
+    cache = PagedKVCache(g.layers, g.num_blocks, g.block_size, g.kv_heads, g.head_dim, g.dtype, device,
+                         host_slots=host_slots)
+    setup_pool_s = time.perf_counter() - t0
+    fill_random_bytes(cache._k_store, 100 + rank)
+    fill_random_bytes(cache._v_store, 200 + rank)
+    config.update({"host_slots": host_slots, "host_pool_bytes": host_slots * slot_bytes, "pool_note": pool_note,
+                   "host_pool_layout": "[slot][layer][K|V][block] (2 MiB-class contiguous per slot)",
+                   "numa_node": pkg.memory.device_numa_node(), "pool_setup_s": round(setup_pool_s, 2)})
+
+    n_sets = args.warmup + args.steps
+    gen = torch.Generator().manual_seed(1234 + rank)
+    sets = []
+    for _ in range(n_sets):
+        out_ids = torch.randperm(g.num_blocks, generator=gen)[:g.n_swap]
+        slots = torch.randperm(host_slots, generator=gen)[:g.n_swap]
+        in_ids = torch.randperm(g.num_blocks, generator=gen)[:g.n_swap]
+        sets.append((out_ids, slots, in_ids))
+    dev_sets = [tuple(t.to(device) for t in s) for s in sets]
+    pin_sets = [tuple(t.pin_memory() for t in s) for s in sets]
+
+    pcie = measure_pcie_peak(cache._host_raw.view(torch.uint8), device) if rank == 0 else None
+    barrier()
+
+    # ---- value leg: ids resident on the device, kernels only -----------------------------
+    def run_value():
+        evs = []
+        for s in range(n_sets):
+            o_ids, slots, i_ids = dev_sets[s]
+            if s == args.warmup:
+                barrier()
+                t_start.record()
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            cache.swap_out(o_ids, slots, aiv=aiv, mover=mover)
+            e[1].record()
+            cache.swap_in(i_ids, slots, aiv=aiv, mover=mover)
+            e[2].record()
+            if s >= args.warmup:
+                evs.append(e)
+        t_end.record()
+        barrier()
+        return evs
+
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    evs = run_value()
+    clocks = sampler.stop() if sampler else None
+    total_ms = max_over_ranks(t_start.elapsed_time(t_end))
+    ms_per_step = total_ms / args.steps
+    out_ms = [e[0].elapsed_time(e[1]) for e in evs]
+    in_ms = [e[1].elapsed_time(e[2]) for e in evs]
+    status = cache.status()
+    value = world * 2 * g.swap_bytes / (ms_per_step * 1e-3) / GB
+
+    # ---- e2e leg: public API, host-resident id lists, status read back every step ------------
+    e2e_start, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    status_host = torch.zeros(1, dtype=torch.int64)
+    for s in range(n_sets):
+        o_ids, slots, i_ids = pin_sets[s]
+        if s == args.warmup:
+            barrier()
+            e2e_start.record()
+        cache.swap_out(o_ids, slots, aiv=aiv, mover=mover)     # ids: pinned host -> device inside the call
+        cache.swap_in(i_ids, slots, aiv=aiv, mover=mover)
+        status_host[0] = cache.status()                         # device -> host read of the step's result
+    e2e_end.record()
+    barrier()
+    e2e_ms = max_over_ranks(e2e_start.elapsed_time(e2e_end)) / args.steps
+    id_bytes = 4 * g.n_swap * 8
+    e2e = {"value": world * 2 * g.swap_bytes / (e2e_ms * 1e-3) / GB, "unit": "GB/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": g.swap_bytes + id_bytes, "d2h_bytes_per_step": g.swap_bytes + 4,
+           "api": "PagedKVCache.swap_out/swap_in -> torch.ops.pcie_through.swap_out/swap_in; payload moves "
+                  "between HBM and the pinned host pool inside the timed region"}
+
+    # ---- gather leg (single-GPU runs) ------------------------------------------------------
+    host_pool_keepalive = cache  # noqa: F841
+    gather = None
+    if world == 1 and not args.no_gather and g.name != "tiny":
+        del cache, host_pool_keepalive, dev_sets
+        torch.cuda.empty_cache()
+        gather = bench_gather(device, max(args.steps, 5), args.warmup, mover,
+                              args.gather_aiv if args.gather_aiv > 0 else None)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except OSError:
+        pass
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    hbm_src = "MEASURED_PEAKS.json hbm_gbs (of measured)" if peaks else "6650 GB/s (of fallback)"
+    out_gbs = g.swap_bytes / (statistics.mean(out_ms) * 1e-3) / GB
+    in_gbs = g.swap_bytes / (statistics.mean(in_ms) * 1e-3) / GB
+    achieved = 2 * g.swap_bytes / ((statistics.mean(out_ms) + statistics.mean(in_ms)) * 1e-3) / GB
+    pcie_peak = (pcie["h2d"] + pcie["d2h"]) / 2
+    roofline = {"bound": "pcie", "kernel": "kv_swap_*_kernel (swap-out and swap-in launches)",
+                "achieved": achieved, "peak": pcie_peak, "unit": "GB/s", "frac": achieved / pcie_peak,
+                "traffic": None,
+                "peak_source": "live cudaMemcpyAsync of 1 GiB pinned<->device, best of 5, mean of the two "
+                               "directions (MEASURED_PEAKS.json holds no PCIe figure)",
+                "swap_out": {"achieved": out_gbs, "peak": pcie["d2h"], "frac": out_gbs / pcie["d2h"]},
+                "swap_in": {"achieved": in_gbs, "peak": pcie["h2d"], "frac": in_gbs / pcie["h2d"]},
+                "nominal_gen5_x16": 63.0, "algorithmic_bytes_per_launch": g.swap_bytes}
+    line = {"metric": "kv_swap_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u8", "data": "synthetic", "config": config,
+            "per_gpu": value / world, "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline,
+            "clocks": clocks, "status_word": status, "mover": args.mover, "aiv": args.aiv or "default",
+            "pcie_memcpy_peak": pcie}
+    if gather is not None:
+        gather["roofline"] = {"bound": "hbm", "kernel": "paged_gather_*_kernel", "achieved": gather["value"],
+                              "peak": hbm_peak, "unit": "GB/s", "frac": gather["value"] / hbm_peak,
+                              "traffic": None, "peak_source": hbm_src, "nominal": 8000.0}
+        line["gather"] = gather
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_swap(g, 3, 1)
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,157 @@
+"""Caller-side shim: how a KV-offload connector of a serving engine drives the ops.
+
+The reference has no serving engine; its test sketches the caller: build the
+per-layer pointer table once on the CPU and move it to the device
+(pcieThrough/tests/test_transfer_kernel.py:42-47), allocate the host pool with
+``memory.alloc_numa_pinned_tensor`` (:28-34) and alternate streams per transfer
+(:50-72).  ``PagedKVCache`` holds exactly that state for a vLLM-style cache —
+per layer one K and one V tensor ``[num_blocks, block_size, kv_heads, head_dim]``
+— and forwards to ``torch.ops.pcie_through.*``.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+import heterofusedkernels_b200 as _pkg
+
+
+class PagedKVCache:
+    """Device caches + pointer tables + (optionally) a pinned, device-mapped host pool.
+
+    Host pool layout: ``[host_slots, layers, 2, block_size, kv_heads, head_dim]`` —
+    one slot holds every layer's K and V of a block contiguously, like the
+    reference's host block that holds all layers (test_transfer_kernel.py:28).
+    """
+
+    def __init__(self, layers: int, num_blocks: int, block_size: int, kv_heads: int, head_dim: int,
+                 dtype: torch.dtype, device: torch.device | str = "cuda", host_slots: int = 0,
+                 k_caches: Optional[Sequence[torch.Tensor]] = None,
+                 v_caches: Optional[Sequence[torch.Tensor]] = None):
+        _pkg.load_ops()
+        self.layers, self.num_blocks, self.block_size = layers, num_blocks, block_size
+        self.kv_heads, self.head_dim, self.dtype = kv_heads, head_dim, dtype
+        self.device = torch.device(device)
+        shape = (num_blocks, block_size, kv_heads, head_dim)
+        if k_caches is None:
+            # one allocation per side keeps the layers adjacent; each layer is its own view
+            self._k_store = torch.empty((layers,) + shape, dtype=dtype, device=self.device)
+            self._v_store = torch.empty((layers,) + shape, dtype=dtype, device=self.device)
+            k_caches, v_caches = list(self._k_store.unbind(0)), list(self._v_store.unbind(0))
+        self.k_caches: List[torch.Tensor] = list(k_caches)
+        self.v_caches: List[torch.Tensor] = list(v_caches)
+        assert len(self.k_caches) == layers and len(self.v_caches) == layers
+        for t in self.k_caches + self.v_caches:
+            assert t.is_cuda and t.is_contiguous() and tuple(t.shape) == shape and t.dtype == dtype
+        # pointer tables: built on the CPU, moved once (test_transfer_kernel.py:42-47)
+        self.k_ptrs_cpu = torch.tensor([t.data_ptr() for t in self.k_caches], dtype=torch.int64)
+        self.v_ptrs_cpu = torch.tensor([t.data_ptr() for t in self.v_caches], dtype=torch.int64)
+        self.k_ptrs = self.k_ptrs_cpu.to(self.device)
+        self.v_ptrs = self.v_ptrs_cpu.to(self.device)
+        self.elt = self.k_caches[0].element_size()
+        self.token_bytes = kv_heads * head_dim * self.elt
+        self.block_bytes = block_size * self.token_bytes
+        self.host_slots = host_slots
+        self.host_pool: Optional[torch.Tensor] = None
+        self._host_raw: Optional[torch.Tensor] = None
+        if host_slots > 0:
+            self.attach_host_pool(host_slots)
+
+    # -- host pool -------------------------------------------------------------
+    def attach_host_pool(self, host_slots: int) -> torch.Tensor:
+        with torch.cuda.device(self.device):
+            raw = _pkg.memory.alloc_numa_pinned_tensor(host_slots * self.layers * 2 * self.block_bytes)
+        self._host_raw = raw
+        self.host_slots = host_slots
+        self.host_pool = raw.view(self.dtype).view(host_slots, self.layers, 2, self.block_size,
+                                                   self.kv_heads, self.head_dim)
+        return self.host_pool
+
+    def swap_bytes(self, n_blocks: int) -> int:
+        return n_blocks * self.layers * 2 * self.block_bytes
+
+    # -- ops ---------------------------------------------------------------------
+    def _ids(self, ids) -> torch.Tensor:
+        if not torch.is_tensor(ids):
+            ids = torch.tensor(list(ids), dtype=torch.int64)
+        return ids.to(self.device, non_blocking=True)
+
+    def swap_out(self, device_block_ids, host_slot_ids, aiv: Optional[int] = None,
+                 mover: Optional[int] = None) -> None:
+        """host_pool[slot] <- cache[block], every layer, K and V, one launch, current stream."""
+        torch.ops.pcie_through.swap_out(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
+                                        self._ids(host_slot_ids), self.num_blocks, None, aiv, mover)
+
+    def swap_in(self, device_block_ids, host_slot_ids, aiv: Optional[int] = None,
+                mover: Optional[int] = None) -> None:
+        """cache[block] <- host_pool[slot], every layer, K and V, one launch, current stream."""
+        torch.ops.pcie_through.swap_in(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
+                                       self._ids(host_slot_ids), self.num_blocks, None, aiv, mover)
+
+    def swap_out_copy_engine(self, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor) -> None:
+        torch.ops.pcie_through.swap_out_copy_engine(self.k_ptrs_cpu, self.v_ptrs_cpu, self.host_pool,
+                                                    device_block_ids.cpu(), host_slot_ids.cpu(), self.num_blocks)
+
+    def swap_in_copy_engine(self, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor) -> None:
+        torch.ops.pcie_through.swap_in_copy_engine(self.k_ptrs_cpu, self.v_ptrs_cpu, self.host_pool,
+                                                   device_block_ids.cpu(), host_slot_ids.cpu(), self.num_blocks)
+
+    def paged_gather(self, block_tables: torch.Tensor, seq_lens: torch.Tensor,
+                     k_out: Optional[torch.Tensor] = None, v_out: Optional[torch.Tensor] = None,
+                     total_tokens: Optional[int] = None, aiv: Optional[int] = None,
+                     mover: Optional[int] = None):
+        """Gathers every layer's pages of the batch into [layers, total_tokens, kv_heads, head_dim]."""
+        if k_out is None:
+            if total_tokens is None:
+                total_tokens = int(seq_lens.sum().item())
+            shape = (self.layers, total_tokens, self.kv_heads, self.head_dim)
+            k_out = torch.empty(shape, dtype=self.dtype, device=self.device)
+            v_out = torch.empty(shape, dtype=self.dtype, device=self.device)
+        torch.ops.pcie_through.paged_gather(self.k_ptrs, self.v_ptrs, k_out, v_out,
+                                            block_tables.to(self.device), seq_lens.to(self.device),
+                                            self.block_size, self.num_blocks, None, aiv, mover)
+        return k_out, v_out
+
+    def status(self) -> int:
+        """Reads and clears the device status word (bits HFK_DEV_* of hfk_b200.h)."""
+        with torch.cuda.device(self.device):
+            return int(torch.ops.pcie_through.device_status())
+
+
+class LayerwisePrefetcher:
+    """Layer-wise prefetch pipeline: while layer l computes on the caller's stream,
+    the blocks of layer l+1 are swapped in on a side stream and other blocks are
+    swapped out on a second one; events order the swap before the layer that needs it.
+
+    One single-layer view of the cache is made per layer (pointer tables of length 1),
+    so each call moves only that layer's K and V.
+    """
+
+    def __init__(self, cache: PagedKVCache):
+        self.cache = cache
+        self.in_stream = torch.cuda.Stream(device=cache.device, priority=-1)
+        self.out_stream = torch.cuda.Stream(device=cache.device, priority=-1)
+        self.k_ptrs = [cache.k_ptrs[l:l + 1] for l in range(cache.layers)]
+        self.v_ptrs = [cache.v_ptrs[l:l + 1] for l in range(cache.layers)]
+        self.pools = [cache.host_pool[:, l:l + 1] for l in range(cache.layers)]
+        self.ready = [torch.cuda.Event() for _ in range(cache.layers)]
+
+    def prefetch(self, layer: int, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor,
+                 aiv: Optional[int] = None, mover: Optional[int] = None) -> torch.cuda.Event:
+        c = self.cache
+        with torch.cuda.stream(self.in_stream):
+            torch.ops.pcie_through.swap_in(self.k_ptrs[layer], self.v_ptrs[layer], self.pools[layer],
+                                           device_block_ids, host_slot_ids, c.num_blocks, None, aiv, mover)
+            self.ready[layer].record()
+        return self.ready[layer]
+
+    def evict(self, layer: int, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor,
+              aiv: Optional[int] = None, mover: Optional[int] = None) -> None:
+        c = self.cache
+        with torch.cuda.stream(self.out_stream):
+            torch.ops.pcie_through.swap_out(self.k_ptrs[layer], self.v_ptrs[layer], self.pools[layer],
+                                            device_block_ids, host_slot_ids, c.num_blocks, None, aiv, mover)
+
+    def wait(self, layer: int) -> None:
+        torch.cuda.current_stream(self.cache.device).wait_event(self.ready[layer])

@@ -1,0 +1,224 @@
+"""Host-side checks of the C ABI that need no GPU: exported symbols, struct layout,
+argument validation (every failing path returns before any CUDA call) and the registry."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "hfk_b200.h").read_text()
+
+
+def declared_functions():
+    body = re.sub(r"/\*.*?\*/", "", HEADER, flags=re.S)
+    return sorted(set(re.findall(r"\b(hfk_[a-z0-9_]+)\s*\(", body)))
+
+
+def test_library_exports_every_declared_symbol(hfk):
+    lib = hfk.lib()
+    names = declared_functions()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/hfk_b200.h but not exported"
+    assert set(names) == set(hfk.PROTOTYPES), "ctypes prototypes and header disagree"
+
+
+def test_error_codes_and_defines_match_header(hfk):
+    for name, val in re.findall(r"#define (HFK_[A-Z0-9_]+) \(?(0x[0-9a-f]+|-?\d+)u?\)?", HEADER):
+        if hasattr(hfk, name):
+            assert getattr(hfk, name) == int(val, 0), name
+    assert hfk.HFK_MAX_SEQS == int(re.search(r"#define HFK_MAX_SEQS (\d+)", HEADER).group(1))
+    assert hfk.lib().hfk_strerror(hfk.HFK_ERR_ALIGNMENT).decode().startswith("address or size")
+    assert hfk.lib().hfk_version().decode().count(".") == 2
+
+
+def test_struct_layouts_follow_the_header_order(hfk):
+    for struct, cname in ((hfk.SwapDesc, "hfk_swap_desc"), (hfk.PagedGatherDesc, "hfk_paged_gather_desc")):
+        m = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), HEADER, flags=re.S)
+        body = re.sub(r"/\*.*?\*/", "", m.group(1), flags=re.S)
+        fields = [re.split(r"[\s\*]+", f.strip())[-1] for f in body.split(";") if f.strip()]
+        assert fields == [f[0] for f in struct._fields_]
+
+
+def _swap_desc(hfk, **over):
+    d = hfk.SwapDesc()
+    buf = torch.zeros(64, dtype=torch.int64)
+    d.k_layer_ptrs = d.v_layer_ptrs = d.device_block_ids = d.host_slot_ids = buf.data_ptr()
+    d.host_pool = 0x10000
+    d.ids_are_int64, d.layers, d.n_blocks = 1, 2, 4
+    d.block_bytes = d.device_block_stride = 4096
+    d.host_slot_stride, d.host_layer_stride, d.host_kv_stride = 16384, 8192, 4096
+    d.num_device_blocks = d.num_host_slots = 8
+    for k, v in over.items():
+        setattr(d, k, v)
+    return d, buf
+
+
+@pytest.mark.parametrize("over,code", [
+    (dict(host_pool=0), "HFK_ERR_INVALID_ARG"), (dict(layers=0), "HFK_ERR_INVALID_ARG"),
+    (dict(n_blocks=-1), "HFK_ERR_INVALID_ARG"), (dict(block_bytes=4008), "HFK_ERR_ALIGNMENT"),
+    (dict(host_kv_stride=4104), "HFK_ERR_ALIGNMENT"), (dict(host_pool=0x10008), "HFK_ERR_ALIGNMENT"),
+    (dict(device_block_stride=2048), "HFK_ERR_INVALID_ARG"), (dict(num_host_slots=0), "HFK_ERR_INVALID_ARG"),
+    (dict(device_block_ids=0), "HFK_ERR_INVALID_ARG"), (dict(layers=5000), "HFK_ERR_TOO_LARGE")])
+def test_swap_validation_errors(hfk, over, code):
+    d, _keep = _swap_desc(hfk, **over)
+    for fn in (hfk.lib().hfk_swap_out, hfk.lib().hfk_swap_in):
+        assert fn(C.byref(d), hfk.MOVER_AUTO, 0, None) == getattr(hfk, code)
+    assert hfk.last_error() != ""
+    assert hfk.lib().hfk_swap_copy_engine(C.byref(d), 1, None) == getattr(hfk, code)
+
+
+def test_swap_unknown_mover_and_null_descriptor(hfk):
+    assert hfk.lib().hfk_swap_out(None, 0, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    d, _keep = _swap_desc(hfk)
+    assert hfk.lib().hfk_swap_in(C.byref(d), 9, 0, None) == hfk.HFK_ERR_INVALID_ARG
+
+
+def test_copy_engine_rejects_out_of_range_ids_on_the_host(hfk):
+    d, buf = _swap_desc(hfk)
+    buf[:4] = torch.tensor([0, 1, 99, 2])
+    assert hfk.lib().hfk_swap_copy_engine(C.byref(d), 0, None) == hfk.HFK_ERR_INVALID_ARG
+    assert "out of range" in hfk.last_error()
+
+
+def _gather_desc(hfk, **over):
+    d = hfk.PagedGatherDesc()
+    buf = torch.zeros(64, dtype=torch.int64)
+    d.k_layer_ptrs = d.v_layer_ptrs = d.block_tables = d.seq_lens = buf.data_ptr()
+    d.k_out, d.v_out = 0x20000, 0x30000
+    d.ids_are_int64, d.layers, d.num_seqs = 1, 2, 2
+    d.max_blocks_per_seq = d.block_table_stride = 4
+    d.block_size, d.token_bytes = 16, 256
+    d.device_block_stride = 4096
+    d.out_layer_stride = 256 * 100
+    d.num_device_blocks, d.total_tokens = 8, 100
+    for k, v in over.items():
+        setattr(d, k, v)
+    return d, buf
+
+
+@pytest.mark.parametrize("over,code", [
+    (dict(k_out=0), "HFK_ERR_INVALID_ARG"), (dict(token_bytes=250), "HFK_ERR_ALIGNMENT"),
+    (dict(num_seqs=5000), "HFK_ERR_TOO_LARGE"), (dict(block_table_stride=2), "HFK_ERR_INVALID_ARG"),
+    (dict(device_block_stride=2048), "HFK_ERR_INVALID_ARG"), (dict(v_out=0x30004), "HFK_ERR_ALIGNMENT"),
+    (dict(out_layer_stride=256), "HFK_ERR_INVALID_ARG"), (dict(block_size=0), "HFK_ERR_INVALID_ARG")])
+def test_paged_gather_validation_errors(hfk, over, code):
+    d, _keep = _gather_desc(hfk, **over)
+    assert hfk.lib().hfk_paged_gather(C.byref(d), hfk.MOVER_AUTO, 0, None) == getattr(hfk, code)
+
+
+def test_group_r_validation_errors(hfk):
+    lib = hfk.lib()
+    assert lib.hfk_gather(None, 0x1000, 0x2000, 1, 4, 64, 0, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    assert lib.hfk_gather(0x1000, 0x2000, 0x3000, 1, 4, 0, 0, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    assert lib.hfk_gather(0x1000, 0x2000, None, 1, 0, 64, 0, 0, None) == hfk.HFK_OK  # nothing to do
+    # head_dim*elt not a multiple of 16 bytes; the reference wants 32-byte multiples
+    # (pcieThrough/csrc/host/tiling/multi_layer_block_transfer.cpp:49-54)
+    assert lib.hfk_multi_layer_block_transfer(0x1000, 0x2000, 16, 2, 1, 24, 1, 0, None) == hfk.HFK_ERR_ALIGNMENT
+    assert lib.hfk_multi_layer_block_transfer(None, 0x2000, 16, 2, 1, 32, 1, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    assert lib.hfk_multi_layer_block_transfer(0x1000, 0x2000, 0, 2, 1, 32, 1, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    assert lib.hfk_fused_memcpy_multi_layer_block_transfer(0x1000, 0x2000, None, 16, 2, 1, 32, 1, 0, None) \
+        == hfk.HFK_ERR_INVALID_ARG
+    assert lib.hfk_set_bulk_geometry(100, 4) == hfk.HFK_ERR_INVALID_ARG
+    assert lib.hfk_set_bulk_geometry(65536, 8) == hfk.HFK_ERR_TOO_LARGE
+    assert lib.hfk_set_bulk_geometry(0, 0) == hfk.HFK_OK
+
+
+# ---- registry (managed_mem.cpp semantics) under the test driver ----------------
+@pytest.fixture()
+def registry(hfk):
+    lib = hfk.lib()
+    lib.hfk_unregister_all()
+    lib.hfk_registry_set_test_driver(1)
+    yield lib
+    lib.hfk_unregister_all()
+    lib.hfk_registry_set_test_driver(0)
+
+
+def test_registry_range_lookup_duplicates_and_removal(registry):
+    lib = registry
+    a = torch.zeros(4096, dtype=torch.uint8)
+    b = torch.zeros(8192, dtype=torch.uint8)
+    pa, pb = a.data_ptr(), b.data_ptr()
+    alias_a = lib.hfk_register_ptr(pa, a.numel())
+    assert alias_a and lib.hfk_registry_count() == 1
+    assert lib.hfk_register_ptr(pa, a.numel()) == alias_a and lib.hfk_registry_count() == 1  # same base twice
+    lib.hfk_register_ptr(pb, b.numel())
+    assert lib.hfk_registry_count() == 2
+    # interior pointers translate by offset; one-past-the-end does not
+    assert lib.hfk_get_device_ptr(pa + 100) == alias_a + 100
+    assert lib.hfk_get_device_ptr(pb + 8191) != 0
+    assert lib.hfk_get_device_ptr(pb + 8192) in (0, lib.hfk_get_device_ptr(pb + 8192))  # may fall in a's range
+    assert lib.hfk_get_record_size(pb + 5) == 8192
+    assert lib.hfk_get_device_ptr(0) == 0 and lib.hfk_get_record_size(None) == 0
+    assert lib.hfk_unregister_ptr(pa) == 0 and lib.hfk_registry_count() == 1
+    assert lib.hfk_get_device_ptr(pa + 100) == 0 or pb <= pa + 100 < pb + 8192
+    assert lib.hfk_unregister_ptr(pa) == 0          # unknown pointer: not an error (managed_mem.cpp:110-113)
+    assert lib.hfk_register_ptr(None, 16) is None   # null / zero size are rejected (managed_mem.cpp:46)
+    assert lib.hfk_register_ptr(pa, 0) is None
+    lib.hfk_unregister_all()
+    assert lib.hfk_registry_count() == 0
+
+
+def test_numa_pinned_allocation_is_zeroed_registered_and_freed(registry, hfk):
+    lib = registry
+    n = 3 << 20
+    p = lib.hfk_alloc_pinned_numa_ptr(n, -1)
+    assert p, hfk.last_error()
+    buf = (C.c_uint8 * n).from_address(p)
+    t = torch.frombuffer(buf, dtype=torch.uint8)
+    assert int(t.sum()) == 0
+    assert lib.hfk_get_record_size(p + n - 1) == n and lib.hfk_get_device_ptr(p + 7) == p + 7
+    del t, buf
+    assert lib.hfk_free_pinned_numa_ptr(p) == 0
+    assert lib.hfk_get_device_ptr(p) == 0
+    assert lib.hfk_free_pinned_numa_ptr(p) == hfk.HFK_ERR_INVALID_ARG  # not ours any more
+    assert lib.hfk_alloc_pinned_numa_ptr(0, -1) is None
+
+
+def test_numa_bind_to_node_zero_or_clean_failure(registry, hfk):
+    p = registry.hfk_alloc_pinned_numa_ptr(1 << 20, 0)
+    if p:
+        assert registry.hfk_free_pinned_numa_ptr(p) == 0
+    else:
+        assert "mbind" in hfk.last_error()
+    assert registry.hfk_alloc_pinned_numa_ptr(1 << 20, 900) is None  # no such node: mbind refuses
+
+
+def test_memory_module_surface(registry):
+    """heterofusedkernels.memory keeps the reference's three names (common/csrc/pybind.cpp:7-11)."""
+    from heterofusedkernels_b200 import build
+
+    build.build_all()
+    from heterofusedkernels import memory
+
+    t = torch.empty(1000, 16, dtype=torch.float16)
+    alias = memory.host_register(t)
+    assert alias == t.data_ptr()  # test driver: identity alias
+    assert memory.get_device_ptr(t.data_ptr() + 32) == alias + 32
+    assert memory.get_device_ptr(12345) == 0
+    memory.host_unregister(t)
+    assert memory.get_device_ptr(t.data_ptr()) == 0
+
+
+def test_torch_ops_are_registered_with_reference_schemas():
+    from heterofusedkernels_b200 import build
+
+    build.build_all()
+    import pcie_through  # noqa: F401  (loads the operator library, like the reference)
+
+    schema = str(torch.ops.pcie_through.gather.default._schema)
+    assert schema == "pcie_through::gather(Tensor gmEmbed, Tensor gmEmbedDst, Tensor gmIds, int? aiv=None) -> ()"
+    schema = str(torch.ops.pcie_through.multi_layer_block_transfer.default._schema)
+    assert schema == ("pcie_through::multi_layer_block_transfer(Tensor deviceBlockCachePtrs, "
+                      "Tensor hostBlockCache, int? aiv=None) -> ()")
+    schema = str(torch.ops.pcie_through.fused_memcpy_multi_layer_block_transfer.default._schema)
+    assert schema == ("pcie_through::fused_memcpy_multi_layer_block_transfer(Tensor deviceBlockCachePtrs, "
+                      "Tensor hostBlockCache, Tensor stagingBlockCache, int? aiv=None) -> ()")
+    for name in ("swap_out", "swap_in", "paged_gather", "swap_out_copy_engine", "swap_in_copy_engine"):
+        assert hasattr(torch.ops.pcie_through, name)
+    # no CPU implementation of any kernel: an all-CPU call is refused by the dispatcher
+    with pytest.raises(NotImplementedError):
+        torch.ops.pcie_through.gather(torch.zeros(4, 4), torch.zeros(2, 4), torch.zeros(2, dtype=torch.long))
