@@ -40,10 +40,19 @@ int cuda_fail(cudaError_t e, const char *what) {
 // ---- tuning state ----------------------------------------------------------
 std::atomic<int> g_stage_bytes{0}, g_n_stages{0}, g_vec_threads{0}, g_vec_unroll{0};
 
-constexpr int kDefaultStageBytes = 32768;
-constexpr int kDefaultStages = 6;
 constexpr int kMaxDynSmem = 227 * 1024;
-constexpr int kSmCount = 148;
+
+// SM count of the current device (148 on B200), cached per device ordinal.
+static int sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int v = cached[dev].load();
+  if (v > 0) return v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+  cached[dev] = v;
+  return v;
+}
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -53,11 +62,11 @@ struct BulkPlan {
 };
 // Ring geometry of the bulk mover for a copy unit of `unit_bytes`, leaving
 // `tables_bytes` of shared memory for the id / prefix tables.
-static BulkPlan plan_bulk(int64_t unit_bytes, size_t tables_bytes) {
+static BulkPlan plan_bulk(int64_t unit_bytes, size_t tables_bytes, int def_stage_bytes, int def_stages) {
   BulkPlan p;
-  p.stage_bytes = g_stage_bytes.load() > 0 ? g_stage_bytes.load() : kDefaultStageBytes;
+  p.stage_bytes = g_stage_bytes.load() > 0 ? g_stage_bytes.load() : def_stage_bytes;
   if (unit_bytes < p.stage_bytes) p.stage_bytes = (int)((unit_bytes + 127) / 128 * 128);
-  p.n_stages = g_n_stages.load() > 0 ? g_n_stages.load() : kDefaultStages;
+  p.n_stages = g_n_stages.load() > 0 ? g_n_stages.load() : def_stages;
   const size_t fixed = sizeof(PumpSmem) + tables_bytes + 256;
   while (p.n_stages > kPumpLag + 1 && (size_t)p.stage_bytes * p.n_stages + fixed > kMaxDynSmem)
     --p.n_stages;
@@ -148,7 +157,7 @@ static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t s
     return HFK_OK;
   }
   if (mover == HFK_MOVER_BULK) {
-    const BulkPlan p = plan_bulk(d->block_bytes, tables);
+    const BulkPlan p = plan_bulk(d->block_bytes, tables, kSwapStageBytes, kSwapStages);
     if (ctas <= 0) ctas = kDefaultSwapCtasBulk;
     const int64_t pieces = (d->block_bytes + p.stage_bytes - 1) / p.stage_bytes;
     if (ctas > items * pieces) ctas = (int)(items * pieces);
@@ -225,7 +234,7 @@ static int gather_impl(const hfk_paged_gather_desc *d, int mover, int ctas, cuda
   a.total_tokens = d->total_tokens;
   if (mover == HFK_MOVER_AUTO) mover = kDefaultMoverGather;
   if (mover == HFK_MOVER_VECTOR) {
-    if (ctas <= 0) ctas = kDefaultGatherCtasVector;
+    if (ctas <= 0) ctas = sm_count() * kGatherVectorCtasPerSm;
     const int th = g_vec_threads.load(), un = g_vec_unroll.load();
     cudaError_t e;
     if (th == 0 || (th == 256 && un == 8)) e = launch_gather_vector<256, 8>(a, ctas, stream);
@@ -238,8 +247,8 @@ static int gather_impl(const hfk_paged_gather_desc *d, int mover, int ctas, cuda
     return HFK_OK;
   }
   if (mover == HFK_MOVER_BULK) {
-    const BulkPlan p = plan_bulk(d->block_size * d->token_bytes, sizeof(GatherTables));
-    if (ctas <= 0) ctas = kDefaultGatherCtasBulk;
+    const BulkPlan p = plan_bulk(d->block_size * d->token_bytes, sizeof(GatherTables), kGatherStageBytes, kGatherStages);
+    if (ctas <= 0) ctas = sm_count();
     auto k = paged_gather_bulk_kernel;
     cudaError_t e = allow_smem(k, p.smem);
     if (e != cudaSuccess) return cuda_fail(e, "paged_gather_bulk_kernel attribute");

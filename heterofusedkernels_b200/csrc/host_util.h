@@ -13,13 +13,21 @@ int cuda_fail(cudaError_t e, const char *what);
 // in the torch ops).  The swap defaults are sized to fill one PCIe Gen5 x16
 // link while occupying a small part of the 148 SMs; the gather defaults to fill
 // HBM.
-constexpr int kDefaultMoverOut = 1;      // HFK_MOVER_VECTOR
-constexpr int kDefaultMoverIn = 1;       // HFK_MOVER_VECTOR
-constexpr int kDefaultMoverGather = 1;   // HFK_MOVER_VECTOR
-constexpr int kDefaultSwapCtasVector = 32;
-constexpr int kDefaultSwapCtasBulk = 16;
-constexpr int kDefaultGatherCtasVector = 148 * 8;
-constexpr int kDefaultGatherCtasBulk = 148;
+//
+// Measured on a B200 behind PCIe Gen5 x16 (cudaMemcpyAsync peak 55.5 GB/s h2d, 57.2 GB/s d2h):
+// the bulk mover reaches the link's plateau for kernel-issued traffic (51.5 GB/s in,
+// 52.7 GB/s out) from 2 single-warp CTAs with a 16 KiB x 8 ring, the vector mover needs 4-8
+// CTAs of 512 threads; 4 CTAs leave a margin.  The paged gather reaches the device's copy
+// bandwidth (6.67 TB/s) with one single-warp CTA per SM and a 32 KiB x 4 ring; more stages in
+// flight were slower (6.2 TB/s with 6), and the best vector geometry gave 6.2 TB/s.
+constexpr int kDefaultMoverOut = 2;      // HFK_MOVER_BULK
+constexpr int kDefaultMoverIn = 2;       // HFK_MOVER_BULK
+constexpr int kDefaultMoverGather = 2;   // HFK_MOVER_BULK
+constexpr int kDefaultSwapCtasVector = 16;
+constexpr int kDefaultSwapCtasBulk = 4;
+constexpr int kSwapStageBytes = 16384, kSwapStages = 8;
+constexpr int kGatherStageBytes = 32768, kGatherStages = 4;
+constexpr int kGatherVectorCtasPerSm = 2;  // vector mover: 256 threads x 8 loads, 2 CTAs per SM
 constexpr int kDefaultRowGatherCtas = 32;
 constexpr int kDefaultTransferCtas = 32;
 
