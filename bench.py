@@ -251,9 +251,10 @@ def main() -> None:
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    from heterofusedkernels_b200 import ranks
+
+    ctx = ranks.RankContext.from_env()
+    rank, local_rank, world = ctx.rank, ctx.local_rank, ctx.world
     g = geometry(args.workload)
     config = {"workload": g.name, "layers": g.layers, "block_size": g.block_size, "kv_heads": g.kv_heads,
               "head_dim": g.head_dim, "kv_dtype": str(g.dtype).replace("torch.", ""),
@@ -280,23 +281,8 @@ def main() -> None:
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist  # noqa: F811
-
-        dist.init_process_group("nccl", device_id=device)
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(x: float) -> float:
-        if dist is None:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    ctx.init("nccl", device)
+    barrier, max_over_ranks = ctx.barrier, ctx.max_over_ranks
 
     mover = {"auto": None, "vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK}[args.mover]
     aiv = args.aiv if args.aiv > 0 else None
@@ -304,11 +290,7 @@ def main() -> None:
     # ---- workload state (outside every timed region) -----------------------------------
     slot_bytes = g.layers * 2 * g.block_bytes
     host_slots = args.host_slots or g.host_slots
-    budget = int(mem_available_bytes() * 0.6 / max(world, 1))
-    pool_note = ""
-    if host_slots * slot_bytes > budget:
-        host_slots = max(2 * g.n_swap, budget // slot_bytes)
-        pool_note = f"host pool shrunk to {host_slots} slots (MemAvailable), transferred set unchanged"
+    host_slots, pool_note = ranks.host_pool_slots(host_slots, slot_bytes, g.n_swap, world, mem_available_bytes())
     t0 = time.perf_counter()
     cache = PagedKVCache(g.layers, g.num_blocks, g.block_size, g.kv_heads, g.head_dim, g.dtype, device,
                          host_slots=host_slots)
@@ -320,13 +302,7 @@ def main() -> None:
                    "numa_node": pkg.memory.device_numa_node(), "pool_setup_s": round(setup_pool_s, 2)})
 
     n_sets = args.warmup + args.steps
-    gen = torch.Generator().manual_seed(1234 + rank)
-    sets = []
-    for _ in range(n_sets):
-        out_ids = torch.randperm(g.num_blocks, generator=gen)[:g.n_swap]
-        slots = torch.randperm(host_slots, generator=gen)[:g.n_swap]
-        in_ids = torch.randperm(g.num_blocks, generator=gen)[:g.n_swap]
-        sets.append((out_ids, slots, in_ids))
+    sets = ranks.rank_id_sets(rank, n_sets, g.n_swap, g.num_blocks, host_slots)
     dev_sets = [tuple(t.to(device) for t in s) for s in sets]
     pin_sets = [tuple(t.pin_memory() for t in s) for s in sets]
 
@@ -362,7 +338,7 @@ def main() -> None:
     out_ms = [e[0].elapsed_time(e[1]) for e in evs]
     in_ms = [e[1].elapsed_time(e[2]) for e in evs]
     status = cache.status()
-    value = world * 2 * g.swap_bytes / (ms_per_step * 1e-3) / GB
+    value = ranks.aggregate_gbs(2 * g.swap_bytes, world, ms_per_step)
 
     # ---- e2e leg: public API, host-resident id lists, status read back every step ------------
     e2e_start, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -394,8 +370,7 @@ def main() -> None:
                               args.gather_aiv if args.gather_aiv > 0 else None)
 
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        ctx.close()
         return
 
     peaks = {}
@@ -431,8 +406,7 @@ def main() -> None:
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_swap(g, 3, 1)
     print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    ctx.close()
 
 
 if __name__ == "__main__":

@@ -1,0 +1,66 @@
+"""The N>1 host logic on CPU: two gloo ranks exercise the barrier, the max-over-ranks reduction,
+the per-rank id lists and the aggregate — the same RankContext bench.py uses with NCCL."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from heterofusedkernels_b200 import ranks
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    ctx = ranks.RankContext.from_env().init("gloo")
+    ctx.barrier()
+    local_ms = 10.0 + 5.0 * rank          # rank 1 is the slow one
+    worst = ctx.max_over_ranks(local_ms)
+    sets = ranks.rank_id_sets(rank, 3, 8, 64, 32)
+    ctx.barrier()
+    q.put((rank, worst, [tuple(t.tolist() for t in s) for s in sets]))
+    ctx.close()
+
+
+def test_two_ranks_take_the_max_time_and_disjoint_seeds():
+    world, port = 2, _free_port()
+    ctxm = mp.get_context("spawn")
+    q = ctxm.Queue()
+    procs = [ctxm.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert [g[1] for g in got] == [15.0, 15.0]            # both ranks see the slowest rank's time
+    assert got[0][2] != got[1][2]                          # ranks do not share id lists
+    for _, _, sets in got:
+        for out_ids, slots, in_ids in sets:
+            assert len(set(out_ids)) == 8 and len(set(slots)) == 8 and len(set(in_ids)) == 8
+            assert max(out_ids) < 64 and max(slots) < 32
+    # whole-job throughput: all ranks' bytes over the slowest rank's time
+    assert ranks.aggregate_gbs(10**9, 2, 15.0) == pytest.approx(2 * 10**9 / 15e-3 / 1e9)
+
+
+def test_single_rank_context_needs_no_process_group():
+    ctx = ranks.RankContext(0, 0, 1).init("gloo")
+    ctx.barrier()
+    assert ctx.max_over_ranks(3.5) == 3.5 and ctx.dist is None
+
+
+def test_host_pool_is_shrunk_per_rank_but_never_below_the_transferred_set():
+    slot = 2 << 20
+    assert ranks.host_pool_slots(40000, slot, 512, 1, 200 << 30) == (40000, "")
+    slots, note = ranks.host_pool_slots(40000, slot, 512, 8, 200 << 30)
+    assert slots == int((200 << 30) * 0.6 / 8) // slot and "shrunk" in note
+    assert ranks.host_pool_slots(40000, slot, 512, 8, 1 << 30)[0] == 1024
