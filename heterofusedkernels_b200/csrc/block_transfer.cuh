@@ -26,7 +26,7 @@ struct TransferArgs {
 
 template <int kThreads, int kUnroll>
 __global__ void __launch_bounds__(kThreads) block_transfer_kernel(TransferArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char **lp = reinterpret_cast<unsigned char **>(smem_raw);
   for (int l = threadIdx.x; l < a.layers; l += kThreads)
     lp[l] = static_cast<unsigned char *>(a.layer_ptrs[l]);

@@ -74,7 +74,7 @@ __device__ __forceinline__ void stage_ids(const SwapArgs &a, SwapTables *t, int6
 // slot front to back.
 template <bool kToHost, int kThreads, int kUnroll>
 __global__ void __launch_bounds__(kThreads) kv_swap_vector_kernel(SwapArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   SwapTables *t = reinterpret_cast<SwapTables *>(smem_raw);
   unsigned char **lp = reinterpret_cast<unsigned char **>(smem_raw + sizeof(SwapTables));
   stage_layer_ptrs(a, lp);

@@ -124,7 +124,7 @@ __device__ __forceinline__ PageCopy locate_page(const GatherArgs &a, const Gathe
 // consecutive pages of one layer's output, i.e. the grid streams the output.
 template <int kThreads, int kUnroll>
 __global__ void __launch_bounds__(kThreads) paged_gather_vector_kernel(GatherArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   GatherTables *t = reinterpret_cast<GatherTables *>(smem_raw);
   build_walk_tables(a, t);
   __syncthreads();
