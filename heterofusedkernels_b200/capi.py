@@ -30,6 +30,7 @@ HFK_DEV_WAIT_TIMEOUT = 0x10
 
 MOVER_AUTO, MOVER_VECTOR, MOVER_BULK = 0, 1, 2
 HFK_MAX_SEQS = 1024
+HFK_STATIC_STAGING_BYTES = 8 * 1024 * 1024
 
 
 class SwapDesc(C.Structure):
@@ -102,6 +103,9 @@ PROTOTYPES = {
     "hfk_fused_memcpy_multi_layer_block_transfer": (
         C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                   C.c_int64, C.c_int, C.c_void_p]),
+    "hfk_fused_memcpy_multi_layer_block_transfer_static": (
+        C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int,
+                  C.c_void_p]),
     "hfk_swap_out": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_int, C.c_void_p]),
     "hfk_swap_in": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_int, C.c_void_p]),
     "hfk_swap_copy_engine": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_void_p]),

@@ -10,6 +10,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 
 #include "block_transfer.cuh"
@@ -456,6 +457,83 @@ int hfk_fused_memcpy_multi_layer_block_transfer(void *const *device_layer_ptrs,
   // ... stage 2: the same kernel, reading the staging buffer (:105)
   return transfer_impl(device_layer_ptrs, staging, block_size, layers, heads, head_dim, elt_size,
                        ctas, stream);
+}
+
+// ---- staged transfer for callers that cannot allocate -------------------------
+//
+// Who this is for.  A KV-offload connector runs inside a serving engine that handed
+// nearly all free HBM to the paged KV cache at start-up and calls the transfer from
+// its scheduling loop: a cudaMalloc there can fail for lack of memory, and even when
+// it succeeds it synchronises the whole device and so stalls the layer compute the
+// transfer is meant to overlap.  Hosts that bind this library over an FFI (cgo, JNI,
+// ctypes) are in the same position for a different reason: they hold pointers to the
+// cache and to the pinned pool, but they own no CUDA allocator from which a staging
+// tensor could come.  For them the staging block lives inside the library.
+//
+// The staging block is one file-scope device array of HFK_STATIC_STAGING_BYTES.
+// Every GPU on which this library runs a kernel holds that much memory until the
+// process exits.  In host code the array's name only stands for the symbol — it is
+// not an address the device can use — so the address is looked up once per device
+// with cudaGetSymbolAddress, with that device current, and cached.
+static __device__ __align__(256) unsigned char g_static_staging[HFK_STATIC_STAGING_BYTES];
+
+namespace hfk {
+constexpr int kMaxDevices = 64;
+static std::mutex g_staging_mu;
+static void *g_staging_addr[kMaxDevices];  // device address of g_static_staging, per device ordinal
+
+// Address of the staging array on the current device; looked up on first use.
+static int static_staging_for_current_device(void **out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(HFK_ERR_UNSUPPORTED, "static staging: device ordinal %d beyond %d", dev, kMaxDevices);
+  std::lock_guard<std::mutex> g(g_staging_mu);
+  if (g_staging_addr[dev] == nullptr) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_staging);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static staging)");
+    if (p == nullptr) return fail(HFK_ERR_CUDA, "static staging: symbol address is null");
+    g_staging_addr[dev] = p;
+  }
+  *out = g_staging_addr[dev];
+  return HFK_OK;
+}
+}  // namespace hfk
+
+int hfk_fused_memcpy_multi_layer_block_transfer_static(void *const *device_layer_ptrs,
+                                                       const void *host_block, int64_t block_size,
+                                                       int64_t layers, int64_t heads,
+                                                       int64_t head_dim, int64_t elt_size, int ctas,
+                                                       hfk_stream_t stream) {
+  if (!host_block)
+    return fail(HFK_ERR_INVALID_ARG, "fused_memcpy_multi_layer_block_transfer_static: null host block");
+  if (block_size <= 0 || layers <= 0 || heads <= 0 || head_dim <= 0 || elt_size <= 0)
+    return fail(HFK_ERR_INVALID_ARG, "fused_memcpy_multi_layer_block_transfer_static: non-positive geometry");
+  // overflow-safe size check against the fixed capacity
+  const uint64_t cap = HFK_STATIC_STAGING_BYTES;
+  uint64_t bytes = 1;
+  const int64_t dims[5] = {block_size, layers, heads, head_dim, elt_size};
+  for (int i = 0; i < 5; ++i) {
+    if ((uint64_t)dims[i] > cap || bytes * (uint64_t)dims[i] > cap)
+      return fail(HFK_ERR_TOO_LARGE,
+                  "fused_memcpy_multi_layer_block_transfer_static: block of [%lld,%lld,%lld,%lld] x %lld bytes "
+                  "exceeds the built-in staging block of %llu bytes; use "
+                  "hfk_fused_memcpy_multi_layer_block_transfer with a staging buffer of your own",
+                  (long long)block_size, (long long)layers, (long long)heads, (long long)head_dim,
+                  (long long)elt_size, (unsigned long long)cap);
+    bytes *= (uint64_t)dims[i];
+  }
+  void *staging = nullptr;
+  int rc = static_staging_for_current_device(&staging);
+  if (rc != HFK_OK) return rc;
+  // Nothing in the staging block has to start at zero: the first `bytes` bytes are
+  // overwritten by this copy before the kernel reads exactly those bytes.
+  cudaError_t e = cudaMemcpyAsync(staging, host_block, (size_t)bytes, cudaMemcpyHostToDevice, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(static staging)");
+  return transfer_impl(device_layer_ptrs, staging, block_size, layers, heads, head_dim, elt_size, ctas,
+                       stream);
 }
 
 }  // extern "C"

@@ -173,6 +173,39 @@ int hfk_fused_memcpy_multi_layer_block_transfer(void *const *device_layer_ptrs,
                                                 int64_t elt_size, int ctas,
                                                 hfk_stream_t stream);
 
+/* Capacity of the staging block built into the library (8 MiB: the reference test's
+ * largest block, [1024, 64, 1, 128] int8 — pcieThrough/tests/test_transfer_kernel.py:15-24). */
+#define HFK_STATIC_STAGING_BYTES (8u * 1024u * 1024u)
+
+/* The staged transfer above for callers that cannot allocate device memory.  It has
+ * no counterpart in the reference.
+ *
+ * Meant for two kinds of caller: a KV-offload connector inside a serving engine that
+ * gave nearly all HBM to the KV cache at start-up (a cudaMalloc in its scheduling loop
+ * may fail, and always synchronises the device, stalling the compute the transfer
+ * should overlap), and FFI hosts (cgo, JNI, ctypes) that hold pointers to the cache and
+ * the pinned pool but own no CUDA allocator to make a staging tensor from.
+ *
+ * Same arguments and result as hfk_fused_memcpy_multi_layer_block_transfer without
+ * `staging`: the staging block is a device array of HFK_STATIC_STAGING_BYTES inside the
+ * library.  Every GPU the library runs on holds that memory until the process exits.
+ * A block larger than that (block_size*layers*heads*head_dim*elt_size) is rejected with
+ * HFK_ERR_TOO_LARGE.  The call allocates nothing: no cudaMalloc, cudaFree or other
+ * allocating routine.
+ *
+ * The first call on each device looks the array's device address up (with that device
+ * current) and caches it; make that first call before any stream capture begins.
+ * All calls on a device share the one staging block, which still holds the previous
+ * call's block: calls must not overlap on the GPU — issue them on one stream, or order
+ * them with events — otherwise they race on the staging bytes.  Nothing in the block
+ * needs clearing between calls: each call overwrites the bytes it then reads. */
+int hfk_fused_memcpy_multi_layer_block_transfer_static(void *const *device_layer_ptrs,
+                                                       const void *host_block,
+                                                       int64_t block_size, int64_t layers,
+                                                       int64_t heads, int64_t head_dim,
+                                                       int64_t elt_size, int ctas,
+                                                       hfk_stream_t stream);
+
 /* ======================================================================== *
  *  Group N — multi-block, all-layer K/V swap and paged gather
  *  (no counterpart function in the reference; conventions follow

@@ -26,10 +26,12 @@ def test_library_exports_every_declared_symbol(hfk):
 
 
 def test_error_codes_and_defines_match_header(hfk):
-    for name, val in re.findall(r"#define (HFK_[A-Z0-9_]+) \(?(0x[0-9a-f]+|-?\d+)u?\)?", HEADER):
+    for name, val in re.findall(r"^#define (HFK_[A-Z0-9_]+) \(?(0x[0-9a-f]+|-?\d+)u?\)?\s*(?:/\*.*)?$", HEADER, flags=re.M):
         if hasattr(hfk, name):
             assert getattr(hfk, name) == int(val, 0), name
     assert hfk.HFK_MAX_SEQS == int(re.search(r"#define HFK_MAX_SEQS (\d+)", HEADER).group(1))
+    m = re.search(r"#define HFK_STATIC_STAGING_BYTES \((\d+)u \* (\d+)u \* (\d+)u\)", HEADER)
+    assert hfk.HFK_STATIC_STAGING_BYTES == int(m.group(1)) * int(m.group(2)) * int(m.group(3))
     assert hfk.lib().hfk_strerror(hfk.HFK_ERR_ALIGNMENT).decode().startswith("address or size")
     assert hfk.lib().hfk_version().decode().count(".") == 2
 
