@@ -327,31 +327,40 @@ def bench_overlap(g, device, args, pkg) -> dict:
                 "out_gbs": layer_bytes / (statistics.median(t_out) * 1e-3) / GB,
                 "in_ms_median": statistics.median(t_in), "out_ms_median": statistics.median(t_out)}
 
-    for _ in range(3):
+    # The GEMM runs under the 1 kW power cap, so its time drifts by several percent as the part
+    # warms up.  Warm up for about two seconds, then alternate alone / overlapped passes and compare
+    # medians taken over the same stretch of time.
+    t_warm = time.perf_counter()
+    while time.perf_counter() - t_warm < 2.0:
         gemm_pass()
     sampler = ClockSampler(device.index or 0)
-    alone = [gemm_pass() for _ in range(5)]
-    t_alone = statistics.median(alone)
     variants = []
+    alone_all = []
+    reps = 7
     for kind, ctas in (("bulk", 2), ("bulk", 4), ("bulk", 8), ("vector", 4), ("vector", 8), ("vector", 16),
                        ("copy_engine", 0)):
         overlapped(kind, ctas)  # warm-up
-        runs = [overlapped(kind, ctas) for _ in range(3)]
-        best = min(runs, key=lambda r: r["main_ms"])
+        alone, runs = [], []
+        for _ in range(reps if kind != "copy_engine" else 3):
+            alone.append(gemm_pass())
+            runs.append(overlapped(kind, ctas))
+        alone_all += alone
+        t_a = statistics.median(alone)
         med_main = statistics.median(r["main_ms"] for r in runs)
         solo = swap_only(kind, ctas)
-        variants.append({"mover": kind, "ctas_per_direction": ctas, "gemm_ms_overlapped": med_main,
-                         "gemm_slowdown_pct": 100.0 * (med_main / t_alone - 1.0),
+        variants.append({"mover": kind, "ctas_per_direction": ctas, "gemm_ms_alone": t_a,
+                         "gemm_ms_overlapped": med_main, "gemm_slowdown_pct": 100.0 * (med_main / t_a - 1.0),
                          "swap_in_gbs": statistics.median(r["in_gbs"] for r in runs),
                          "swap_out_gbs": statistics.median(r["out_gbs"] for r in runs),
-                         "swap_in_gbs_no_gemm": solo["in_gbs"], "swap_out_gbs_no_gemm": solo["out_gbs"],
-                         "best_main_ms": best["main_ms"]})
+                         "swap_in_gbs_no_gemm": solo["in_gbs"], "swap_out_gbs_no_gemm": solo["out_gbs"]})
+    t_alone = statistics.median(alone_all)
     t_alone2 = statistics.median([gemm_pass() for _ in range(3)])
     clocks = sampler.stop()
     status = cache.status()
-    pick = min((v for v in variants if v["mover"] != "copy_engine"), key=lambda v: v["gemm_slowdown_pct"])
+    ok = [v for v in variants if v["mover"] != "copy_engine" and v["gemm_slowdown_pct"] < 10.0]
+    pick = max(ok or variants, key=lambda v: v["swap_in_gbs"] + v["swap_out_gbs"])
     return {"metric": "kv_swap_GBps_under_gemm_overlap", "value": (pick["swap_in_gbs"] + pick["swap_out_gbs"]) / 2,
-            "unit": "GB/s", "n_gpus": 1, "steps": 3, "warmup": 1, "ms_per_step": pick["gemm_ms_overlapped"],
+            "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": 1, "ms_per_step": pick["gemm_ms_overlapped"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": {"workload": g.name, "layers": L, "blocks_per_layer_per_direction": g.n_swap,
                        "bytes_per_layer_per_direction": layer_bytes, "kv_dtype": "float8_e4m3fn",
@@ -360,7 +369,7 @@ def bench_overlap(g, device, args, pkg) -> dict:
                        "pool sizes": "8192 device / 16384 host blocks (not fixed by the configuration; chosen here)"},
             "gemm_alone_ms": t_alone, "gemm_alone_ms_after": t_alone2, "gemm_alone_tflops": L * flops / (t_alone * 1e-3) / 1e12,
             "picked": pick, "variants": variants, "clocks": clocks, "status_word": status,
-            "gpu_launches": 2 * L * 3}
+            "gpu_launches": 2 * L * reps}
 
 
 # --------------------------------------------------------------------------- main
