@@ -54,6 +54,26 @@ class SwapDesc(C.Structure):
     ]
 
 
+class RelayoutDesc(C.Structure):
+    """struct hfk_relayout_desc"""
+    _fields_ = [
+        ("layer_ptrs", C.c_void_p),
+        ("host_pool", C.c_void_p),
+        ("device_block_ids", C.c_void_p),
+        ("host_slot_ids", C.c_void_p),
+        ("ids_are_int64", C.c_int),
+        ("layers", C.c_int),
+        ("n_blocks", C.c_int64),
+        ("block_size", C.c_int64),
+        ("heads", C.c_int64),
+        ("head_bytes", C.c_int64),
+        ("device_block_stride", C.c_int64),
+        ("host_slot_stride", C.c_int64),
+        ("num_device_blocks", C.c_int64),
+        ("num_host_slots", C.c_int64),
+    ]
+
+
 class PagedGatherDesc(C.Structure):
     """struct hfk_paged_gather_desc"""
     _fields_ = [
@@ -84,6 +104,7 @@ PROTOTYPES = {
     "hfk_version": (C.c_char_p, []),
     "hfk_device_status": (C.c_int, [C.POINTER(C.c_uint), C.c_void_p]),
     "hfk_set_bulk_geometry": (C.c_int, [C.c_int, C.c_int]),
+    "hfk_set_bulk_lag": (C.c_int, [C.c_int]),
     "hfk_set_vector_geometry": (C.c_int, [C.c_int, C.c_int]),
     "hfk_register_ptr": (C.c_void_p, [C.c_void_p, C.c_size_t]),
     "hfk_unregister_ptr": (C.c_int, [C.c_void_p]),
@@ -109,6 +130,7 @@ PROTOTYPES = {
     "hfk_swap_out": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_int, C.c_void_p]),
     "hfk_swap_in": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_int, C.c_void_p]),
     "hfk_swap_copy_engine": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_void_p]),
+    "hfk_swap_relayout": (C.c_int, [C.POINTER(RelayoutDesc), C.c_int, C.c_int, C.c_void_p]),
     "hfk_paged_gather": (C.c_int, [C.POINTER(PagedGatherDesc), C.c_int, C.c_int, C.c_void_p]),
 }
 

@@ -139,7 +139,11 @@ struct CopyDesc {
   uint32_t bytes;  // 0 = nothing to do (skipped unit)
 };
 
-constexpr int kPumpLag = 2;  // stores allowed to be still reading shared memory
+// kLag (template parameter of the pump) = how many of the most recent stores may still be
+// reading their stage when the next load is issued; the remaining n_stages - kLag stages hold
+// loads in flight.  Compiled values:
+constexpr int kPumpLagDefault = 2;
+constexpr int kPumpLagMax = 8;
 
 struct PumpSmem {
   uint64_t full[32];      // one mbarrier per stage (kStages <= 32)
@@ -147,7 +151,7 @@ struct PumpSmem {
 };
 
 // make_desc(k) returns the descriptor of this CTA's k-th unit, k < total.
-template <typename MakeDesc>
+template <int kPumpLag, typename MakeDesc>
 __device__ __forceinline__ void run_pump(PumpSmem *ps, unsigned char *stages, int stage_bytes,
                                          int n_stages, int64_t total, uint32_t &seq,
                                          MakeDesc make_desc) {

@@ -12,12 +12,14 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <type_traits>
 
 #include "block_transfer.cuh"
 #include "common.cuh"
 #include "host_util.h"
 #include "kv_swap.cuh"
 #include "paged_gather.cuh"
+#include "relayout_swap.cuh"
 #include "row_gather.cuh"
 
 namespace hfk {
@@ -39,7 +41,7 @@ int cuda_fail(cudaError_t e, const char *what) {
 }
 
 // ---- tuning state ----------------------------------------------------------
-std::atomic<int> g_stage_bytes{0}, g_n_stages{0}, g_vec_threads{0}, g_vec_unroll{0};
+std::atomic<int> g_stage_bytes{0}, g_n_stages{0}, g_bulk_lag{0}, g_vec_threads{0}, g_vec_unroll{0};
 
 constexpr int kMaxDynSmem = 227 * 1024;
 
@@ -58,22 +60,41 @@ static int sm_count() {
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct BulkPlan {
-  int stage_bytes, n_stages;
+  int stage_bytes, n_stages, lag;
   size_t smem;
 };
 // Ring geometry of the bulk mover for a copy unit of `unit_bytes`, leaving
 // `tables_bytes` of shared memory for the id / prefix tables.
-static BulkPlan plan_bulk(int64_t unit_bytes, size_t tables_bytes, int def_stage_bytes, int def_stages) {
+static BulkPlan plan_bulk(int64_t unit_bytes, size_t tables_bytes, int def_stage_bytes, int def_stages,
+                          int def_lag) {
   BulkPlan p;
   p.stage_bytes = g_stage_bytes.load() > 0 ? g_stage_bytes.load() : def_stage_bytes;
   if (unit_bytes < p.stage_bytes) p.stage_bytes = (int)((unit_bytes + 127) / 128 * 128);
   p.n_stages = g_n_stages.load() > 0 ? g_n_stages.load() : def_stages;
   const size_t fixed = sizeof(PumpSmem) + tables_bytes + 256;
-  while (p.n_stages > kPumpLag + 1 && (size_t)p.stage_bytes * p.n_stages + fixed > kMaxDynSmem)
-    --p.n_stages;
+  while (p.n_stages > 2 && (size_t)p.stage_bytes * p.n_stages + fixed > kMaxDynSmem) --p.n_stages;
   if (p.n_stages > 32) p.n_stages = 32;
+  p.lag = g_bulk_lag.load() > 0 ? g_bulk_lag.load() : def_lag;
+  if (p.lag > p.n_stages - 1) p.lag = p.n_stages - 1;  // at least one load in flight
+  if (p.lag == 5) p.lag = 4;                            // compiled: 1, 2, 3, 4, 6, 8
+  if (p.lag == 7) p.lag = 6;
+  if (p.lag > kPumpLagMax) p.lag = kPumpLagMax;
   p.smem = (size_t)p.stage_bytes * p.n_stages + fixed;
   return p;
+}
+
+// Calls f(std::integral_constant<int, lag>) for the compiled lag values.
+template <typename F>
+static cudaError_t launch_by_lag(int lag, F f) {
+  switch (lag) {
+    case 1: return f(std::integral_constant<int, 1>{});
+    case 2: return f(std::integral_constant<int, 2>{});
+    case 3: return f(std::integral_constant<int, 3>{});
+    case 4: return f(std::integral_constant<int, 4>{});
+    case 6: return f(std::integral_constant<int, 6>{});
+    case 8: return f(std::integral_constant<int, 8>{});
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 template <typename K>
@@ -158,15 +179,17 @@ static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t s
     return HFK_OK;
   }
   if (mover == HFK_MOVER_BULK) {
-    const BulkPlan p = plan_bulk(d->block_bytes, tables, kSwapStageBytes, kSwapStages);
+    const BulkPlan p = plan_bulk(d->block_bytes, tables, kSwapStageBytes, kSwapStages, kSwapLag);
     if (ctas <= 0) ctas = kDefaultSwapCtasBulk;
     const int64_t pieces = (d->block_bytes + p.stage_bytes - 1) / p.stage_bytes;
     if (ctas > items * pieces) ctas = (int)(items * pieces);
-    auto k = kv_swap_bulk_kernel<kToHost>;
-    cudaError_t e = allow_smem(k, p.smem);
-    if (e != cudaSuccess) return cuda_fail(e, "kv_swap_bulk_kernel attribute");
-    k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
-    e = cudaGetLastError();
+    cudaError_t e = launch_by_lag(p.lag, [&](auto lag) {
+      auto k = kv_swap_bulk_kernel<kToHost, decltype(lag)::value>;
+      cudaError_t err = allow_smem(k, p.smem);
+      if (err != cudaSuccess) return err;
+      k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
+      return cudaGetLastError();
+    });
     if (e != cudaSuccess) return cuda_fail(e, "kv_swap_bulk_kernel launch");
     return HFK_OK;
   }
@@ -248,17 +271,74 @@ static int gather_impl(const hfk_paged_gather_desc *d, int mover, int ctas, cuda
     return HFK_OK;
   }
   if (mover == HFK_MOVER_BULK) {
-    const BulkPlan p = plan_bulk(d->block_size * d->token_bytes, sizeof(GatherTables), kGatherStageBytes, kGatherStages);
+    const BulkPlan p = plan_bulk(d->block_size * d->token_bytes, sizeof(GatherTables), kGatherStageBytes, kGatherStages,
+                                kGatherLag);
     if (ctas <= 0) ctas = sm_count();
-    auto k = paged_gather_bulk_kernel;
-    cudaError_t e = allow_smem(k, p.smem);
-    if (e != cudaSuccess) return cuda_fail(e, "paged_gather_bulk_kernel attribute");
-    k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
-    e = cudaGetLastError();
+    cudaError_t e = launch_by_lag(p.lag, [&](auto lag) {
+      auto k = paged_gather_bulk_kernel<decltype(lag)::value>;
+      cudaError_t err = allow_smem(k, p.smem);
+      if (err != cudaSuccess) return err;
+      k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
+      return cudaGetLastError();
+    });
     if (e != cudaSuccess) return cuda_fail(e, "paged_gather_bulk_kernel launch");
     return HFK_OK;
   }
   return fail(HFK_ERR_INVALID_ARG, "paged_gather: unknown mover %d", mover);
+}
+
+// ---- re-layout swap ----------------------------------------------------------
+template <bool kToHost>
+static cudaError_t launch_relayout(const RelayoutArgs &a, int ctas, size_t smem, cudaStream_t s) {
+  auto k = kv_relayout_swap_kernel<kToHost, 512, 4>;
+  cudaError_t e = allow_smem(k, smem);
+  if (e != cudaSuccess) return e;
+  k<<<ctas, 512, smem, s>>>(a);
+  return cudaGetLastError();
+}
+
+static int relayout_impl(const hfk_relayout_desc *d, int to_host, int ctas, cudaStream_t stream) {
+  if (!d) return fail(HFK_ERR_INVALID_ARG, "swap_relayout: descriptor is null");
+  if (!d->layer_ptrs || !d->host_pool)
+    return fail(HFK_ERR_INVALID_ARG, "swap_relayout: null pointer table or host pool");
+  if (d->n_blocks < 0 || d->layers <= 0 || d->block_size <= 0 || d->heads <= 0 || d->head_bytes <= 0 ||
+      d->num_device_blocks <= 0 || d->num_host_slots <= 0)
+    return fail(HFK_ERR_INVALID_ARG, "swap_relayout: non-positive geometry");
+  if (d->n_blocks > 0 && (!d->device_block_ids || !d->host_slot_ids))
+    return fail(HFK_ERR_INVALID_ARG, "swap_relayout: null id list");
+  if ((d->head_bytes | d->device_block_stride | d->host_slot_stride) & 15)
+    return fail(HFK_ERR_ALIGNMENT, "swap_relayout: head_bytes and strides must be multiples of 16 bytes");
+  if (!aligned16(d->host_pool)) return fail(HFK_ERR_ALIGNMENT, "swap_relayout: host pool is not 16-byte aligned");
+  if (d->device_block_stride < d->heads * d->block_size * d->head_bytes)
+    return fail(HFK_ERR_INVALID_ARG, "swap_relayout: device_block_stride smaller than one block");
+  if (d->host_slot_stride < d->block_size * d->layers * d->heads * d->head_bytes)
+    return fail(HFK_ERR_INVALID_ARG, "swap_relayout: host_slot_stride smaller than one block");
+  if (d->layers > 4096) return fail(HFK_ERR_TOO_LARGE, "swap_relayout: more than 4096 layers");
+  if (d->n_blocks == 0) return HFK_OK;
+  RelayoutArgs a;
+  a.layer_ptrs = d->layer_ptrs;
+  a.host_pool = static_cast<unsigned char *>(d->host_pool);
+  a.device_block_ids = d->device_block_ids;
+  a.host_slot_ids = d->host_slot_ids;
+  a.ids_are_int64 = d->ids_are_int64;
+  a.layers = d->layers;
+  a.n_blocks = d->n_blocks;
+  a.block_size = d->block_size;
+  a.heads = d->heads;
+  a.d16 = d->head_bytes / 16;
+  a.device_block_stride = d->device_block_stride;
+  a.host_slot_stride = d->host_slot_stride;
+  a.num_device_blocks = d->num_device_blocks;
+  a.num_host_slots = d->num_host_slots;
+  if (ctas <= 0) ctas = kDefaultRelayoutCtas;
+  const int64_t total = d->n_blocks * d->block_size * d->layers * d->heads * a.d16;
+  const int64_t max_ctas = (total + 511) / 512;
+  if (ctas > max_ctas) ctas = (int)max_ctas;
+  const size_t smem = sizeof(RelayoutTables) + sizeof(void *) * (size_t)d->layers;
+  cudaError_t e = to_host ? launch_relayout<true>(a, ctas, smem, stream)
+                          : launch_relayout<false>(a, ctas, smem, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "kv_relayout_swap_kernel launch");
+  return HFK_OK;
 }
 
 // ---- Group R ---------------------------------------------------------------
@@ -362,12 +442,18 @@ int hfk_device_status(unsigned int *status_bits, hfk_stream_t stream) {
   return HFK_OK;
 }
 
+int hfk_set_bulk_lag(int lag) {
+  if (lag < 0 || lag > kPumpLagMax)
+    return fail(HFK_ERR_INVALID_ARG, "bulk lag: 0 (default) .. %d", kPumpLagMax);
+  g_bulk_lag = lag;
+  return HFK_OK;
+}
+
 int hfk_set_bulk_geometry(int stage_bytes, int n_stages) {
   if (stage_bytes < 0 || n_stages < 0 || (stage_bytes & 127) || n_stages > 32 ||
-      (n_stages > 0 && n_stages <= kPumpLag))
-    return fail(HFK_ERR_INVALID_ARG, "bulk geometry: stage_bytes %% 128 == 0, %d < n_stages <= 32",
-                kPumpLag);
-  if ((size_t)stage_bytes * (n_stages > 0 ? n_stages : kPumpLag + 1) > (size_t)kMaxDynSmem - 20480)
+      (n_stages > 0 && n_stages < 2))
+    return fail(HFK_ERR_INVALID_ARG, "bulk geometry: stage_bytes %% 128 == 0, 2 <= n_stages <= 32");
+  if ((size_t)stage_bytes * (n_stages > 0 ? n_stages : 2) > (size_t)kMaxDynSmem - 20480)
     return fail(HFK_ERR_TOO_LARGE, "bulk geometry: ring does not fit shared memory");
   g_stage_bytes = stage_bytes;
   g_n_stages = n_stages;
@@ -422,6 +508,10 @@ int hfk_swap_copy_engine(const hfk_swap_desc *d, int to_host, hfk_stream_t strea
     }
   }
   return HFK_OK;
+}
+
+int hfk_swap_relayout(const hfk_relayout_desc *desc, int to_host, int ctas, hfk_stream_t stream) {
+  return relayout_impl(desc, to_host, ctas, stream);
 }
 
 int hfk_paged_gather(const hfk_paged_gather_desc *desc, int mover, int ctas, hfk_stream_t stream) {

@@ -25,10 +25,11 @@ constexpr int kDefaultMoverIn = 2;       // HFK_MOVER_BULK
 constexpr int kDefaultMoverGather = 2;   // HFK_MOVER_BULK
 constexpr int kDefaultSwapCtasVector = 16;
 constexpr int kDefaultSwapCtasBulk = 4;
-constexpr int kSwapStageBytes = 16384, kSwapStages = 8;
-constexpr int kGatherStageBytes = 32768, kGatherStages = 4;
+constexpr int kSwapStageBytes = 16384, kSwapStages = 8, kSwapLag = 2;
+constexpr int kGatherStageBytes = 32768, kGatherStages = 4, kGatherLag = 2;
 constexpr int kGatherVectorCtasPerSm = 2;  // vector mover: 256 threads x 8 loads, 2 CTAs per SM
 constexpr int kDefaultRowGatherCtas = 32;
 constexpr int kDefaultTransferCtas = 32;
+constexpr int kDefaultRelayoutCtas = 32;
 
 }  // namespace hfk

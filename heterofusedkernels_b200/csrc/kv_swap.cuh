@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(kThreads) kv_swap_vector_kernel(SwapArgs a) {
 // ---- mover 2: one warp per CTA pumping bulk copies -------------------------
 // Unit = one piece (<= stage_bytes) of one chunk.  Shared memory: stages, then
 // PumpSmem, then SwapTables, then the layer pointers.
-template <bool kToHost>
+template <bool kToHost, int kLag>
 __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_bytes,
                                                           int n_stages) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_
     const int64_t units = (int64_t)tn * per_block * pieces;
     // this CTA's units are g = blockIdx.x + k*gridDim.x
     const int64_t mine = units > blockIdx.x ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    run_pump(ps, stages, stage_bytes, n_stages, mine, seq, [&](int64_t k) {
+    run_pump<kLag>(ps, stages, stage_bytes, n_stages, mine, seq, [&](int64_t k) {
       const int64_t g = blockIdx.x + k * (int64_t)gridDim.x;
       const int64_t w = g / pieces;
       const int piece = (int)(g - w * pieces);

@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(kThreads) paged_gather_vector_kernel(GatherArg
 }
 
 // ---- mover 2: one warp per CTA pumping bulk copies -------------------------
+template <int kLag>
 __global__ void __launch_bounds__(32) paged_gather_bulk_kernel(GatherArgs a, int stage_bytes,
                                                                int n_stages) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -164,7 +165,7 @@ __global__ void __launch_bounds__(32) paged_gather_bulk_kernel(GatherArgs a, int
   const int64_t units = pages * 2 * a.layers * pieces;
   const int64_t mine = units > blockIdx.x ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   uint32_t seq = 0;
-  run_pump(ps, stages, stage_bytes, n_stages, mine, seq, [&](int64_t k) {
+  run_pump<kLag>(ps, stages, stage_bytes, n_stages, mine, seq, [&](int64_t k) {
     const int64_t g = blockIdx.x + k * (int64_t)gridDim.x;
     const int64_t w = g / pieces;
     const int piece = (int)(g - w * pieces);

@@ -224,6 +224,61 @@ void swap_in_copy_engine(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerP
   check_rc(hfk_swap_copy_engine(&d, 0, at::cuda::getCurrentCUDAStream().stream()), "swap_in_copy_engine");
 }
 
+// Multi-block swap in the reference's host block format.  hostPool: registered CPU tensor
+// [slots, BlockSize, Layers, Heads, HeadDim] (each slot laid out like hostBlockCache of
+// multi_layer_block_transfer); layerPtrs: device int64 [Layers], layer l's cache being
+// [numDeviceBlocks, Heads, BlockSize, HeadDim].
+static hfk_relayout_desc relayout_desc(const at::Tensor &layerPtrs, const at::Tensor &hostPool,
+                                       const at::Tensor &deviceBlockIds, const at::Tensor &hostSlotIds,
+                                       int64_t numDeviceBlocks, c10::optional<int64_t> deviceBlockStride,
+                                       const char *op) {
+  TORCH_CHECK(hostPool.device().is_cpu() && hostPool.dim() == 5, op,
+              ": hostPool must be a CPU tensor [slots, BlockSize, Layers, Heads, HeadDim]");
+  TORCH_CHECK(hostPool[0].is_contiguous(), op, ": every host slot must be contiguous");
+  const int64_t elt = hostPool.element_size();
+  hfk_relayout_desc d;
+  d.layers = static_cast<int>(hostPool.size(2));
+  check_ptr_table(layerPtrs, d.layers, op, true);
+  d.ids_are_int64 = ids_are_int64(deviceBlockIds, op);
+  TORCH_CHECK(ids_are_int64(hostSlotIds, op) == d.ids_are_int64, op, ": both id lists must have the same dtype");
+  TORCH_CHECK(deviceBlockIds.numel() == hostSlotIds.numel(), op, ": id lists differ in length");
+  TORCH_CHECK(deviceBlockIds.is_cuda() && hostSlotIds.is_cuda(), op, ": id lists must be device tensors");
+  d.layer_ptrs = reinterpret_cast<void *const *>(layerPtrs.data_ptr());
+  d.host_pool = device_accessible(hostPool, op);
+  d.device_block_ids = deviceBlockIds.data_ptr();
+  d.host_slot_ids = hostSlotIds.data_ptr();
+  d.n_blocks = deviceBlockIds.numel();
+  d.block_size = hostPool.size(1);
+  d.heads = hostPool.size(3);
+  d.head_bytes = hostPool.size(4) * elt;
+  d.device_block_stride = deviceBlockStride.has_value() ? deviceBlockStride.value()
+                                                        : d.heads * d.block_size * d.head_bytes;
+  d.host_slot_stride = hostPool.stride(0) * elt;
+  d.num_device_blocks = numDeviceBlocks;
+  d.num_host_slots = hostPool.size(0);
+  return d;
+}
+
+void swap_in_relayout(const at::Tensor &layerPtrs, const at::Tensor &hostPool, const at::Tensor &deviceBlockIds,
+                      const at::Tensor &hostSlotIds, int64_t numDeviceBlocks,
+                      c10::optional<int64_t> deviceBlockStride, c10::optional<int64_t> aiv) {
+  const int ctas = cores_from(aiv);
+  const hfk_relayout_desc d = relayout_desc(layerPtrs, hostPool, deviceBlockIds, hostSlotIds, numDeviceBlocks,
+                                            deviceBlockStride, "swap_in_relayout");
+  const c10::cuda::CUDAGuard guard(layerPtrs.device());
+  check_rc(hfk_swap_relayout(&d, 0, ctas, at::cuda::getCurrentCUDAStream().stream()), "swap_in_relayout");
+}
+
+void swap_out_relayout(const at::Tensor &layerPtrs, const at::Tensor &hostPool, const at::Tensor &deviceBlockIds,
+                       const at::Tensor &hostSlotIds, int64_t numDeviceBlocks,
+                       c10::optional<int64_t> deviceBlockStride, c10::optional<int64_t> aiv) {
+  const int ctas = cores_from(aiv);
+  const hfk_relayout_desc d = relayout_desc(layerPtrs, hostPool, deviceBlockIds, hostSlotIds, numDeviceBlocks,
+                                            deviceBlockStride, "swap_out_relayout");
+  const c10::cuda::CUDAGuard guard(layerPtrs.device());
+  check_rc(hfk_swap_relayout(&d, 1, ctas, at::cuda::getCurrentCUDAStream().stream()), "swap_out_relayout");
+}
+
 // kOut / vOut: [layers, total_tokens, ...token dims]; blockTables: [num_seqs, max_blocks];
 // seqLens: [num_seqs].
 void paged_gather(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs, const at::Tensor &kOut,
@@ -290,6 +345,8 @@ TORCH_LIBRARY_FRAGMENT(pcie_through, m) {
   m.def("swap_out_copy_engine(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None) -> ()");
   m.def("swap_in_copy_engine(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None) -> ()");
   m.def("paged_gather(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor kOut, Tensor vOut, Tensor blockTables, Tensor seqLens, int blockSize, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None, int? mover=None) -> ()");
+  m.def("swap_in_relayout(Tensor layerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None) -> ()");
+  m.def("swap_out_relayout(Tensor layerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None) -> ()");
   m.def("device_status() -> int");
 }
 
@@ -300,6 +357,8 @@ TORCH_LIBRARY_IMPL(pcie_through, CUDA, m) {
   m.impl("swap_out", TORCH_FN(pciethrough::swap_out));
   m.impl("swap_in", TORCH_FN(pciethrough::swap_in));
   m.impl("paged_gather", TORCH_FN(pciethrough::paged_gather));
+  m.impl("swap_in_relayout", TORCH_FN(pciethrough::swap_in_relayout));
+  m.impl("swap_out_relayout", TORCH_FN(pciethrough::swap_out_relayout));
 }
 
 // all-CPU argument lists dispatch here; there is no CPU implementation of any

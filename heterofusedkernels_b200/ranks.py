@@ -52,6 +52,16 @@ class RankContext:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
 
+    def gather_floats(self, values) -> List[List[float]]:
+        """Every rank's vector of floats, in rank order, on every rank (per-GPU figures for the report)."""
+        if self.dist is None:
+            return [[float(v) for v in values]]
+        dev = self.device if self.device is not None else "cpu"
+        mine = torch.tensor([float(v) for v in values], dtype=torch.float64, device=dev)
+        out = [torch.zeros_like(mine) for _ in range(self.world)]
+        self.dist.all_gather(out, mine)
+        return [t.tolist() for t in out]
+
     def close(self) -> None:
         if self.dist is not None and self.dist.is_initialized():
             self.dist.destroy_process_group()

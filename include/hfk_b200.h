@@ -71,6 +71,9 @@ int hfk_device_status(unsigned int *status_bits, hfk_stream_t stream);
  * mover: threads per CTA x 16-byte loads in flight per thread (only a few
  * combinations are compiled).  0 restores the default. */
 int hfk_set_bulk_geometry(int stage_bytes, int n_stages);
+/* Of the ring's stages, how many may hold stores that are still draining (the rest hold
+ * loads in flight); compiled values 1, 2, 3, 4, 6, 8; 0 restores the default. */
+int hfk_set_bulk_lag(int lag);
 int hfk_set_vector_geometry(int threads, int unroll);
 
 /* ======================================================================== *
@@ -254,6 +257,35 @@ int hfk_swap_in(const hfk_swap_desc *desc, int mover, int ctas, hfk_stream_t str
  * host_pool is the HOST address of the pinned pool.  to_host != 0 = swap-out. */
 int hfk_swap_copy_engine(const hfk_swap_desc *desc_with_host_arrays, int to_host,
                          hfk_stream_t stream);
+
+/* Multi-block swap in the reference's host block format: host slot = one KV block
+ * [block_size][layers][heads][head_dim] (pcieThrough/README.md:25-29), layer l of the device
+ * cache = [num_device_blocks][heads][block_size][head_dim].  K and V are separate tensor
+ * families here as in the reference (call once per family, or list them as 2*layers layers). */
+typedef struct hfk_relayout_desc {
+  void *const *layer_ptrs;      /* DEVICE array of `layers` cache bases */
+  void *host_pool;              /* device alias; slot s at host_pool + s*host_slot_stride */
+  const void *device_block_ids; /* DEVICE arrays of n_blocks ids */
+  const void *host_slot_ids;
+  int ids_are_int64;
+  int layers;
+  int64_t n_blocks;
+  int64_t block_size;
+  int64_t heads;
+  int64_t head_bytes;           /* head_dim*elt_size; multiple of 16 */
+  int64_t device_block_stride;  /* >= heads*block_size*head_bytes */
+  int64_t host_slot_stride;     /* >= block_size*layers*heads*head_bytes */
+  int64_t num_device_blocks;
+  int64_t num_host_slots;
+} hfk_relayout_desc;
+
+/* to_host == 0: for every i, t, l, h:
+ *   layer_ptrs[l][device_block_ids[i]][h][t][:] = host slot(host_slot_ids[i])[t][l][h][:]
+ * (with n_blocks == 1 this is hfk_multi_layer_block_transfer); to_host != 0: the inverse copy.
+ * Generalises multi_layer_block_transfer
+ * (pcieThrough/csrc/kernel/multi_layer_block_transfer_kernel.h:42-82) to id lists and to the
+ * device->host direction. */
+int hfk_swap_relayout(const hfk_relayout_desc *desc, int to_host, int ctas, hfk_stream_t stream);
 
 typedef struct hfk_paged_gather_desc {
   void *const *k_layer_ptrs; /* DEVICE arrays of `layers` cache bases, as in hfk_swap_desc */

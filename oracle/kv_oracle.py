@@ -164,6 +164,28 @@ def swap_in(dev_k: Sequence[torch.Tensor], dev_v: Sequence[torch.Tensor], host_p
         dev_v[l].index_copy_(0, ids, host_pool[:, l, 1].index_select(0, slots))
 
 
+def relayout_swap_in(dev_layers: Sequence[torch.Tensor], host_pool: torch.Tensor,
+                     device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor) -> None:
+    """Multi-block form of the reference's transfer: for every listed block,
+    dev_layers[l][block] ([H,B,D]) = host_pool[slot] ([B,L,H,D]).permute(1,2,0,3)[l]
+    (the permute asserted in pcieThrough/tests/test_transfer_kernel.py:81-83).  In place."""
+    ids, slots = device_block_ids.to(torch.int64), host_slot_ids.to(torch.int64)
+    pool = _u8(host_pool)
+    for l, cache in enumerate(dev_layers):
+        src = pool.index_select(0, slots)[:, :, l].permute(0, 2, 1, 3)   # [n, H, B, D bytes]
+        _u8(cache).index_copy_(0, ids, src.contiguous())
+
+
+def relayout_swap_out(dev_layers: Sequence[torch.Tensor], host_pool: torch.Tensor,
+                      device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor) -> None:
+    """The inverse: host_pool[slot][:, l] = dev_layers[l][block].permute(1,0,2).  In place."""
+    ids, slots = device_block_ids.to(torch.int64), host_slot_ids.to(torch.int64)
+    pool = _u8(host_pool)
+    for l, cache in enumerate(dev_layers):
+        src = _u8(cache).index_select(0, ids).permute(0, 2, 1, 3)        # [n, B, H, D bytes]
+        pool[:, :, l].index_copy_(0, slots, src.contiguous())
+
+
 def paged_gather(dev_k: Sequence[torch.Tensor], dev_v: Sequence[torch.Tensor], block_tables: torch.Tensor,
                  seq_lens: torch.Tensor, block_size: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """Contiguous per-sequence K and V: out[l] = cat_s( cache[l][table[s]].flatten(0,1)[:len_s] ).

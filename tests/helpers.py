@@ -100,3 +100,24 @@ class PinnedPool:
             self.tensor = None
             capi.check(capi.lib().hfk_free_pinned_numa_ptr(self.ptr), "free")
             self.ptr = 0
+
+
+def relayout_desc(layer_ptrs, host_pool: torch.Tensor, host_alias: int, dev_ids, slot_ids, num_device_blocks,
+                  device_block_stride=None) -> capi.RelayoutDesc:
+    """host_pool: CPU tensor [slots, B, L, H, D]."""
+    elt = host_pool.element_size()
+    _, B, L, H, D = host_pool.shape
+    d = capi.RelayoutDesc()
+    d.layer_ptrs = layer_ptrs.data_ptr()
+    d.host_pool = host_alias
+    d.device_block_ids = dev_ids.data_ptr()
+    d.host_slot_ids = slot_ids.data_ptr()
+    d.ids_are_int64 = 1 if dev_ids.dtype == torch.int64 else 0
+    d.layers = L
+    d.n_blocks = dev_ids.numel()
+    d.block_size, d.heads, d.head_bytes = B, H, D * elt
+    d.device_block_stride = device_block_stride or H * B * D * elt
+    d.host_slot_stride = host_pool.stride(0) * elt
+    d.num_device_blocks = num_device_blocks
+    d.num_host_slots = host_pool.shape[0]
+    return d

@@ -12,7 +12,8 @@ import pytest
 import torch
 
 from oracle import kv_oracle as o
-from tests.helpers import PinnedPool, dev_zeros, gather_desc, ptr_table, stream_handle, swap_desc, u8
+from tests.helpers import (PinnedPool, dev_zeros, gather_desc, ptr_table, relayout_desc, stream_handle, swap_desc,
+                           u8)
 
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
@@ -360,3 +361,59 @@ def test_multi_layer_block_transfer_golden(hfk, cuda_device):
                                                        stream_handle()), "transfer")
     torch.cuda.synchronize()
     assert np.array_equal(torch.stack(dev_layers, 0).cpu().numpy(), z["expected"])
+
+
+# ------------------------------------- multi-block swap in the reference's host format ---
+@pytest.mark.parametrize("B,L,H,D,dtype,blocks,slots,n,idt", [
+    (1024, 4, 1, 128, torch.int8, 6, 8, 5, torch.int64),       # the reference's block shape, several blocks
+    (16, 32, 8, 128, torch.bfloat16, 40, 48, 33, torch.int64),  # Llama-3-8B geometry
+    (16, 3, 2, 8, torch.float16, 20, 20, 20, torch.int32),      # 16-byte head rows
+    (4, 2, 1, 4, torch.float32, 2000, 1500, 1200, torch.int64),  # more ids than one shared-memory tile
+])
+def test_relayout_swap_in_and_out_match_oracle(hfk, cuda_device, B, L, H, D, dtype, blocks, slots, n, idt):
+    pool = PinnedPool((slots, B, L, H, D), dtype)
+    try:
+        pool.tensor.copy_(o.random_kv_bytes((slots, B, L, H, D), dtype, seed=3))
+        cpu_pool = pool.tensor.clone()
+        cpu_dev = [o.random_kv_bytes((blocks, H, B, D), dtype, seed=10 + l) for l in range(L)]
+        gpu_dev = [t.to(cuda_device) for t in cpu_dev]
+        ptrs = ptr_table(gpu_dev, cuda_device)
+        ids, sl = o.distinct_ids(n, blocks, 1).to(idt), o.distinct_ids(n, slots, 2).to(idt)
+        d = relayout_desc(ptrs, pool.tensor, pool.alias, ids.to(cuda_device), sl.to(cuda_device), blocks)
+        hfk.check(hfk.lib().hfk_swap_relayout(C.byref(d), 0, 6, stream_handle()), "relayout in")
+        torch.cuda.synchronize()
+        o.relayout_swap_in(cpu_dev, cpu_pool, ids, sl)
+        for g, c in zip(gpu_dev, cpu_dev):
+            assert same_bytes(g, c)
+        # and out again into other slots
+        ids2, sl2 = o.distinct_ids(n, blocks, 4).to(idt), o.distinct_ids(n, slots, 5).to(idt)
+        d = relayout_desc(ptrs, pool.tensor, pool.alias, ids2.to(cuda_device), sl2.to(cuda_device), blocks)
+        hfk.check(hfk.lib().hfk_swap_relayout(C.byref(d), 1, 0, stream_handle()), "relayout out")
+        torch.cuda.synchronize()
+        o.relayout_swap_out(cpu_dev, cpu_pool, ids2, sl2)
+        assert same_bytes(pool.tensor, cpu_pool)
+        assert hfk.device_status() == 0
+    finally:
+        pool.close()
+
+
+def test_relayout_swap_single_block_equals_multi_layer_block_transfer(hfk, cuda_device):
+    """With one block the multi-block op is the reference's operator."""
+    z = np.load(GOLDEN / "block_transfer_int8.npz")
+    host = torch.from_numpy(z["host_block"])
+    B, L, H, D = host.shape
+    pool = PinnedPool((3, B, L, H, D), torch.int8)
+    try:
+        pool.tensor[1].copy_(host)
+        gpu_dev = [dev_zeros((4, H, B, D), torch.int8, cuda_device) for _ in range(L)]
+        ptrs = ptr_table(gpu_dev, cuda_device)
+        ids, sl = torch.tensor([2], device=cuda_device), torch.tensor([1], device=cuda_device)
+        d = relayout_desc(ptrs, pool.tensor, pool.alias, ids, sl, 4)
+        hfk.check(hfk.lib().hfk_swap_relayout(C.byref(d), 0, 0, stream_handle()), "relayout in")
+        bad = relayout_desc(ptrs, pool.tensor, pool.alias, torch.tensor([9], device=cuda_device), sl, 4)
+        hfk.check(hfk.lib().hfk_swap_relayout(C.byref(bad), 0, 0, stream_handle()), "relayout bad id")
+        torch.cuda.synchronize()
+        assert np.array_equal(torch.stack([g[2] for g in gpu_dev], 0).cpu().numpy(), z["expected"])
+        assert hfk.device_status() == hfk.HFK_DEV_BAD_DEVICE_BLOCK_ID
+    finally:
+        pool.close()

@@ -173,3 +173,24 @@ def test_layerwise_prefetcher_moves_single_layers(ops, cuda_device):
     assert torch.equal(u8(cache.host_pool), u8(ref_pool))
     for d, c in zip(cache.k_caches + cache.v_caches, cpu_k + cpu_v):
         assert torch.equal(u8(d.cpu()), u8(c))
+
+
+def test_relayout_swap_ops(ops, cuda_device):
+    op, memory = ops
+    B, L, H, D, slots, blocks, n = 64, 4, 2, 128, 10, 12, 7
+    pool = memory.alloc_numa_pinned_tensor(slots * B * L * H * D * 2).view(torch.bfloat16).view(slots, B, L, H, D)
+    pool.copy_(o.random_kv_bytes((slots, B, L, H, D), torch.bfloat16, seed=1))
+    cpu_pool = pool.clone()
+    cpu_dev = [o.random_kv_bytes((blocks, H, B, D), torch.bfloat16, seed=5 + l) for l in range(L)]
+    gpu_dev = [t.to(cuda_device) for t in cpu_dev]
+    ptrs = torch.tensor([t.data_ptr() for t in gpu_dev], dtype=torch.int64).to(cuda_device)
+    ids, sl = o.distinct_ids(n, blocks, 1), o.distinct_ids(n, slots, 2)
+    op.swap_in_relayout(ptrs, pool, ids.to(cuda_device), sl.to(cuda_device), blocks)
+    o.relayout_swap_in(cpu_dev, cpu_pool, ids, sl)
+    ids2, sl2 = o.distinct_ids(n, blocks, 3), o.distinct_ids(n, slots, 4)
+    op.swap_out_relayout(ptrs, pool, ids2.to(cuda_device), sl2.to(cuda_device), blocks, None, 8)
+    o.relayout_swap_out(cpu_dev, cpu_pool, ids2, sl2)
+    torch.cuda.synchronize()
+    assert torch.equal(u8(pool), u8(cpu_pool))
+    for g, c in zip(gpu_dev, cpu_dev):
+        assert torch.equal(u8(g.cpu()), u8(c))

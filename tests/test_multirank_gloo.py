@@ -26,6 +26,8 @@ def _worker(rank, world, port, q):
     local_ms = 10.0 + 5.0 * rank          # rank 1 is the slow one
     worst = ctx.max_over_ranks(local_ms)
     sets = ranks.rank_id_sets(rank, 3, 8, 64, 32)
+    per_rank = ctx.gather_floats([rank, local_ms])
+    assert per_rank == [[0.0, 10.0], [1.0, 15.0]]
     ctx.barrier()
     q.put((rank, worst, [tuple(t.tolist() for t in s) for s in sets]))
     ctx.close()
@@ -56,6 +58,7 @@ def test_single_rank_context_needs_no_process_group():
     ctx = ranks.RankContext(0, 0, 1).init("gloo")
     ctx.barrier()
     assert ctx.max_over_ranks(3.5) == 3.5 and ctx.dist is None
+    assert ctx.gather_floats([1, 2.5]) == [[1.0, 2.5]]
 
 
 def test_host_pool_is_shrunk_per_rank_but_never_below_the_transferred_set():

@@ -122,3 +122,19 @@ def test_algorithmic_bytes_of_the_benchmark_configurations():
     assert o.CONFIGS["llama3_70b_tp8_swap"].swap_bytes() == 10_737_418_240
     g = o.CONFIGS["qwen2_7b_fp8_prefetch"]
     assert g.n_swap * 2 * g.block_bytes == 4_194_304  # one layer, one direction
+
+
+def test_relayout_swap_is_the_block_transfer_per_block_and_round_trips():
+    B, L, H, D = 8, 3, 2, 32
+    pool = o.random_kv_bytes((6, B, L, H, D), torch.int8, seed=1)
+    dev = [torch.zeros((10, H, B, D), dtype=torch.int8) for _ in range(L)]
+    ids, slots = torch.tensor([7, 2, 9]), torch.tensor([5, 0, 3])
+    o.relayout_swap_in(dev, pool, ids, slots)
+    for i in range(3):
+        lit = o.block_transfer_literal(pool[slots[i]].numpy(), aiv=2)      # the reference kernel, block by block
+        for l in range(L):
+            assert np.array_equal(dev[l][ids[i]].numpy(), lit[l])
+    assert all(int(d[[0, 1, 3, 4, 5, 6, 8]].abs().sum()) == 0 for d in dev)  # other blocks untouched
+    pool2 = torch.zeros_like(pool)
+    o.relayout_swap_out(dev, pool2, ids, slots)
+    assert torch.equal(pool2[slots], pool[slots]) and int(pool2[[1, 2, 4]].abs().sum()) == 0
