@@ -189,6 +189,29 @@ def measure_pcie_peak(pool_u8: torch.Tensor, device) -> dict:
     return res
 
 
+def measure_pcie_concurrent(ctx, pool_u8: torch.Tensor, device) -> dict:
+    """cudaMemcpyAsync rate with EVERY rank copying at the same time: 8 back-to-back copies of 1 GiB per
+    direction after a barrier.  This is the denominator for N > 1: what the host (root complexes, memory)
+    gives N links at once, as opposed to one link alone."""
+    n = min(pool_u8.numel(), 1 << 30)
+    host = pool_u8[:n]
+    dev = torch.empty(n, dtype=torch.uint8, device=device)
+    res = {}
+    for name, dst, src in (("h2d", dev, host), ("d2h", host, dev)):
+        dst.copy_(src, non_blocking=True)
+        ctx.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(8):
+            dst.copy_(src, non_blocking=True)
+        b.record()
+        b.synchronize()
+        res[name] = 8 * n / (a.elapsed_time(b) * 1e-3) / GB
+        ctx.barrier()
+    del dev
+    return res
+
+
 # --------------------------------------------------------------------------- gather leg
 def bench_gather(device, steps: int, warmup: int, mover, aiv, num_seqs: int = 64) -> dict:
     """Paged gather, Llama-3-8B layout: 64 sequences of 512..8192 tokens (seeded), block tables that are
@@ -540,7 +563,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="llama3_8b_swap")
-    ap.add_argument("--mover", default="auto", choices=["auto", "vector", "bulk"])
+    ap.add_argument("--mover", default="auto", choices=["auto", "vector", "bulk", "staged"])
+    ap.add_argument("--staging-mb", type=int, default=1024, help="staging buffer of the staged mover (MiB)")
     ap.add_argument("--aiv", type=int, default=0, help="CTAs per swap kernel (0 = library default)")
     ap.add_argument("--gather-aiv", type=int, default=0)
     ap.add_argument("--host-slots", type=int, default=0, help="override the host pool size (slots)")
@@ -587,7 +611,8 @@ def main() -> None:
     ctx.init("nccl", device)
     barrier, max_over_ranks = ctx.barrier, ctx.max_over_ranks
 
-    mover = {"auto": None, "vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK}[args.mover]
+    mover = {"auto": None, "vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK, "staged": None}[args.mover]
+    staged = args.mover == "staged"
     aiv = args.aiv if args.aiv > 0 else None
 
     if args.gather_only:
@@ -630,6 +655,22 @@ def main() -> None:
 
     pcie = measure_pcie_peak(cache._host_raw.view(torch.uint8), device) if rank == 0 else None
     barrier()
+    pcie_conc = None
+    if world > 1:
+        mine = measure_pcie_concurrent(ctx, cache._host_raw.view(torch.uint8), device)
+        pcie_conc = ctx.gather_floats([mine["h2d"], mine["d2h"]])
+
+    def do_out(dev_ids, slots_dev, slots_cpu):
+        if staged:
+            cache.swap_out_staged(dev_ids, slots_cpu, staging_bytes=args.staging_mb << 20)
+        else:
+            cache.swap_out(dev_ids, slots_dev, aiv=aiv, mover=mover)
+
+    def do_in(dev_ids, slots_dev, slots_cpu):
+        if staged:
+            cache.swap_in_staged(dev_ids, slots_cpu, staging_bytes=args.staging_mb << 20)
+        else:
+            cache.swap_in(dev_ids, slots_dev, aiv=aiv, mover=mover)
 
     # ---- value leg: ids resident on the device, kernels only -----------------------------
     def run_value():
@@ -641,9 +682,9 @@ def main() -> None:
                 t_start.record()
             e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
             e[0].record()
-            cache.swap_out(o_ids, slots, aiv=aiv, mover=mover)
+            do_out(o_ids, slots, sets[s][1])
             e[1].record()
-            cache.swap_in(i_ids, slots, aiv=aiv, mover=mover)
+            do_in(i_ids, slots, sets[s][1])
             e[2].record()
             if s >= args.warmup:
                 evs.append(e)
@@ -675,8 +716,8 @@ def main() -> None:
         if s == args.warmup:
             barrier()
             e2e_start.record()
-        cache.swap_out(o_ids, slots, aiv=aiv, mover=mover)     # ids: pinned host -> device inside the call
-        cache.swap_in(i_ids, slots, aiv=aiv, mover=mover)
+        do_out(o_ids, slots, sets[s][1])     # ids: pinned host -> device inside the call
+        do_in(i_ids, slots, sets[s][1])
         status_host[0] = cache.status()                         # device -> host read of the step's result
     e2e_end.record()
     barrier()
@@ -727,6 +768,8 @@ def main() -> None:
             "per_gpu": value / world, "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline,
             "clocks": clocks, "status_word": status, "mover": args.mover, "aiv": args.aiv or "default",
             "pcie_memcpy_peak": pcie,
+            "pcie_memcpy_concurrent_per_rank": None if pcie_conc is None else
+            [{"rank": i, "h2d": r[0], "d2h": r[1]} for i, r in enumerate(pcie_conc)],
             "per_rank": [{"rank": i, "numa_node": int(r[0]), "pci_bus": "%02x" % int(r[4]), "swap_out_GBps": r[1],
                           "swap_in_GBps": r[2], "ms_per_step": r[3]} for i, r in enumerate(per_rank)],
             "host": {"cpus": os.cpu_count(), "mem_available_GB": round(mem_available_bytes() / 1e9, 1)}}

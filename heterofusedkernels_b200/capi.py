@@ -130,6 +130,8 @@ PROTOTYPES = {
     "hfk_swap_out": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_int, C.c_void_p]),
     "hfk_swap_in": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_int, C.c_void_p]),
     "hfk_swap_copy_engine": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_void_p]),
+    "hfk_swap_staged": (C.c_int, [C.POINTER(SwapDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int,
+                                  C.c_int, C.c_void_p]),
     "hfk_swap_relayout": (C.c_int, [C.POINTER(RelayoutDesc), C.c_int, C.c_int, C.c_void_p]),
     "hfk_paged_gather": (C.c_int, [C.POINTER(PagedGatherDesc), C.c_int, C.c_int, C.c_void_p]),
 }

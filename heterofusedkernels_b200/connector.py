@@ -89,6 +89,27 @@ class PagedKVCache:
         torch.ops.pcie_through.swap_in(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
                                        self._ids(host_slot_ids), self.num_blocks, None, aiv, mover)
 
+    def _staging(self, staging_bytes: int) -> torch.Tensor:
+        slot = self.layers * 2 * self.block_bytes
+        want = max(slot, staging_bytes)
+        if getattr(self, "_staging_buf", None) is None or self._staging_buf.numel() < want:
+            self._staging_buf = torch.empty(want, dtype=torch.uint8, device=self.device)
+        return self._staging_buf
+
+    def swap_out_staged(self, device_block_ids, host_slot_ids_cpu: torch.Tensor, staging_bytes: int = 256 << 20,
+                        aiv: Optional[int] = None) -> None:
+        """Swap-out through the copy engine: a packing kernel into a staging buffer, then one
+        cudaMemcpyAsync per host slot (256-byte PCIe transactions instead of a kernel's 128-byte ones)."""
+        torch.ops.pcie_through.swap_out_staged(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
+                                               host_slot_ids_cpu, self._staging(staging_bytes), self.num_blocks,
+                                               None, aiv)
+
+    def swap_in_staged(self, device_block_ids, host_slot_ids_cpu: torch.Tensor, staging_bytes: int = 256 << 20,
+                       aiv: Optional[int] = None) -> None:
+        torch.ops.pcie_through.swap_in_staged(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
+                                              host_slot_ids_cpu, self._staging(staging_bytes), self.num_blocks,
+                                              None, aiv)
+
     def swap_out_copy_engine(self, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor) -> None:
         torch.ops.pcie_through.swap_out_copy_engine(self.k_ptrs_cpu, self.v_ptrs_cpu, self.host_pool,
                                                     device_block_ids.cpu(), host_slot_ids.cpu(), self.num_blocks)

@@ -6,6 +6,7 @@
 // on CUDA the plan travels as kernel parameters, so nothing is uploaded per call.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -287,6 +288,87 @@ static int gather_impl(const hfk_paged_gather_desc *d, int mover, int ctas, cuda
   return fail(HFK_ERR_INVALID_ARG, "paged_gather: unknown mover %d", mover);
 }
 
+// ---- staged swap through the copy engine ---------------------------------------
+static int swap_staged_impl(const hfk_swap_desc *d, const void *slots_host, void *pool_host, void *staging,
+                            size_t staging_bytes, int to_host, int ctas, cudaStream_t stream) {
+  if (!d) return fail(HFK_ERR_INVALID_ARG, "swap_staged: descriptor is null");
+  hfk_swap_desc probe = *d;
+  probe.host_slot_ids = slots_host;  // only for the null check of the common validation
+  probe.host_pool = pool_host;
+  int rc = validate_swap(&probe);
+  if (rc != HFK_OK) return rc;
+  if (!staging) return fail(HFK_ERR_INVALID_ARG, "swap_staged: staging buffer is null");
+  if (!aligned16(staging)) return fail(HFK_ERR_ALIGNMENT, "swap_staged: staging buffer is not 16-byte aligned");
+  const int64_t slot_bytes = (int64_t)d->layers * 2 * d->block_bytes;
+  if (d->host_kv_stride != d->block_bytes || d->host_layer_stride != 2 * d->block_bytes)
+    return fail(HFK_ERR_UNSUPPORTED,
+                "swap_staged: the host pool must be slot-contiguous ([slot][layer][K|V][block])");
+  if ((int64_t)staging_bytes < slot_bytes)
+    return fail(HFK_ERR_TOO_LARGE, "swap_staged: staging buffer of %zu bytes holds less than one slot (%lld bytes)",
+                staging_bytes, (long long)slot_bytes);
+  if (d->n_blocks == 0) return HFK_OK;
+  auto slot_at = [&](int64_t i) -> int64_t {
+    return d->ids_are_int64 ? static_cast<const int64_t *>(slots_host)[i]
+                            : (int64_t) static_cast<const int32_t *>(slots_host)[i];
+  };
+  for (int64_t i = 0; i < d->n_blocks; ++i)
+    if (slot_at(i) < 0 || slot_at(i) >= d->num_host_slots)
+      return fail(HFK_ERR_INVALID_ARG, "swap_staged: host slot id %lld out of range at %lld",
+                  (long long)slot_at(i), (long long)i);
+  const int64_t per_round = (int64_t)(staging_bytes / (size_t)slot_bytes);
+  const size_t id_width = d->ids_are_int64 ? 8 : 4;
+  if (ctas <= 0) ctas = sm_count();  // the packing kernel is HBM to HBM: spread it over the device
+  unsigned char *pool = static_cast<unsigned char *>(pool_host);
+  unsigned char *stg = static_cast<unsigned char *>(staging);
+  for (int64_t i0 = 0; i0 < d->n_blocks; i0 += per_round) {
+    const int64_t n = std::min(per_round, d->n_blocks - i0);
+    // the packing kernel sees the staging buffer as a dense pool: slot = position in this round
+    hfk_swap_desc k = *d;
+    k.host_pool = staging;
+    k.device_block_ids = static_cast<const unsigned char *>(d->device_block_ids) + (size_t)i0 * id_width;
+    k.host_slot_ids = nullptr;
+    k.n_blocks = n;
+    k.host_slot_stride = slot_bytes;
+    k.num_host_slots = n;
+    const SwapArgs a = to_args(&k);
+    const size_t tables = sizeof(SwapTables) + 2 * sizeof(void *) * (size_t)d->layers;
+    const BulkPlan p = plan_bulk(d->block_bytes, tables, kGatherStageBytes, kGatherStages, kGatherLag);
+    auto pack = [&](bool to_staging) -> cudaError_t {
+      return launch_by_lag(p.lag, [&](auto lag) {
+        cudaError_t err;
+        if (to_staging) {
+          auto kern = kv_swap_bulk_kernel<true, decltype(lag)::value>;
+          if ((err = allow_smem(kern, p.smem)) != cudaSuccess) return err;
+          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
+        } else {
+          auto kern = kv_swap_bulk_kernel<false, decltype(lag)::value>;
+          if ((err = allow_smem(kern, p.smem)) != cudaSuccess) return err;
+          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
+        }
+        return cudaGetLastError();
+      });
+    };
+    cudaError_t e;
+    if (to_host && (e = pack(true)) != cudaSuccess) return cuda_fail(e, "staging pack kernel");
+    // one copy-engine transfer per run of consecutive slots
+    const bool dense_pool = d->host_slot_stride == slot_bytes;
+    for (int64_t i = 0; i < n;) {
+      int64_t j = i + 1;
+      if (dense_pool)
+        while (j < n && slot_at(i0 + j) == slot_at(i0 + j - 1) + 1) ++j;
+      unsigned char *h = pool + slot_at(i0 + i) * d->host_slot_stride;
+      unsigned char *s = stg + i * slot_bytes;
+      const size_t nb = (size_t)(j - i) * (size_t)slot_bytes;
+      e = to_host ? cudaMemcpyAsync(h, s, nb, cudaMemcpyDeviceToHost, stream)
+                  : cudaMemcpyAsync(s, h, nb, cudaMemcpyHostToDevice, stream);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(slot)");
+      i = j;
+    }
+    if (!to_host && (e = pack(false)) != cudaSuccess) return cuda_fail(e, "staging unpack kernel");
+  }
+  return HFK_OK;
+}
+
 // ---- re-layout swap ----------------------------------------------------------
 template <bool kToHost>
 static cudaError_t launch_relayout(const RelayoutArgs &a, int ctas, size_t smem, cudaStream_t s) {
@@ -508,6 +590,12 @@ int hfk_swap_copy_engine(const hfk_swap_desc *d, int to_host, hfk_stream_t strea
     }
   }
   return HFK_OK;
+}
+
+int hfk_swap_staged(const hfk_swap_desc *desc, const void *host_slot_ids_host, void *host_pool_host,
+                    void *staging, size_t staging_bytes, int to_host, int ctas, hfk_stream_t stream) {
+  return swap_staged_impl(desc, host_slot_ids_host, host_pool_host, staging, staging_bytes, to_host, ctas,
+                          stream);
 }
 
 int hfk_swap_relayout(const hfk_relayout_desc *desc, int to_host, int ctas, hfk_stream_t stream) {

@@ -57,7 +57,8 @@ __device__ __forceinline__ void stage_layer_ptrs(const SwapArgs &a, unsigned cha
 __device__ __forceinline__ void stage_ids(const SwapArgs &a, SwapTables *t, int64_t tile0, int tn) {
   for (int i = threadIdx.x; i < tn; i += blockDim.x) {
     const int64_t d = load_id(a.device_block_ids, a.ids_are_int64, tile0 + i);
-    const int64_t h = load_id(a.host_slot_ids, a.ids_are_int64, tile0 + i);
+    // a null slot list means "slot = position in the list" (dense staging buffer)
+    const int64_t h = a.host_slot_ids ? load_id(a.host_slot_ids, a.ids_are_int64, tile0 + i) : tile0 + i;
     const bool d_ok = d >= 0 && d < a.num_device_blocks;
     const bool h_ok = h >= 0 && h < a.num_host_slots;
     if (!d_ok) raise_status(HFK_DEV_BAD_DEVICE_BLOCK_ID);

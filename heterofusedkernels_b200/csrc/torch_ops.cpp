@@ -204,6 +204,42 @@ void swap_in(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs, const a
   check_rc(hfk_swap_in(&d, mover_from(mover), ctas, at::cuda::getCurrentCUDAStream().stream()), "swap_in");
 }
 
+// Staged movers: a packing kernel plus one copy-engine transfer per host slot.  hostSlotIds is a
+// CPU tensor here (the copies are addressed on the host); staging is a device byte buffer of at
+// least one slot.
+static void swap_staged(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs, const at::Tensor &hostPool,
+                        const at::Tensor &deviceBlockIds, const at::Tensor &hostSlotIds, const at::Tensor &staging,
+                        int64_t numDeviceBlocks, c10::optional<int64_t> deviceBlockStride,
+                        c10::optional<int64_t> aiv, int to_host, const char *op) {
+  const int ctas = cores_from(aiv);
+  TORCH_CHECK(hostSlotIds.device().is_cpu(), op, ": hostSlotIds must be a CPU tensor");
+  TORCH_CHECK(staging.is_cuda() && staging.is_contiguous(), op, ": staging must be a contiguous device tensor");
+  // build the descriptor with the device id list standing in for both lists, then attach the host list
+  hfk_swap_desc d = swap_desc(kLayerPtrs, vLayerPtrs, hostPool, deviceBlockIds, deviceBlockIds, numDeviceBlocks,
+                              deviceBlockStride, true, op);
+  TORCH_CHECK(ids_are_int64(hostSlotIds, op) == d.ids_are_int64 && hostSlotIds.numel() == deviceBlockIds.numel(),
+              op, ": hostSlotIds must match deviceBlockIds in dtype and length");
+  const c10::cuda::CUDAGuard guard(kLayerPtrs.device());
+  check_rc(hfk_swap_staged(&d, hostSlotIds.data_ptr(), hostPool.data_ptr(), staging.data_ptr(),
+                           static_cast<size_t>(staging.nbytes()), to_host, ctas,
+                           at::cuda::getCurrentCUDAStream().stream()),
+           op);
+}
+
+void swap_out_staged(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs, const at::Tensor &hostPool,
+                     const at::Tensor &deviceBlockIds, const at::Tensor &hostSlotIds, const at::Tensor &staging,
+                     int64_t numDeviceBlocks, c10::optional<int64_t> deviceBlockStride, c10::optional<int64_t> aiv) {
+  swap_staged(kLayerPtrs, vLayerPtrs, hostPool, deviceBlockIds, hostSlotIds, staging, numDeviceBlocks,
+              deviceBlockStride, aiv, 1, "swap_out_staged");
+}
+
+void swap_in_staged(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs, const at::Tensor &hostPool,
+                    const at::Tensor &deviceBlockIds, const at::Tensor &hostSlotIds, const at::Tensor &staging,
+                    int64_t numDeviceBlocks, c10::optional<int64_t> deviceBlockStride, c10::optional<int64_t> aiv) {
+  swap_staged(kLayerPtrs, vLayerPtrs, hostPool, deviceBlockIds, hostSlotIds, staging, numDeviceBlocks,
+              deviceBlockStride, aiv, 0, "swap_in_staged");
+}
+
 // Copy-engine twins: every tensor argument lives on the CPU (the addresses are
 // formed on the host); the copies run on the current stream of the current device.
 void swap_out_copy_engine(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs,
@@ -345,6 +381,8 @@ TORCH_LIBRARY_FRAGMENT(pcie_through, m) {
   m.def("swap_out_copy_engine(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None) -> ()");
   m.def("swap_in_copy_engine(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None) -> ()");
   m.def("paged_gather(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor kOut, Tensor vOut, Tensor blockTables, Tensor seqLens, int blockSize, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None, int? mover=None) -> ()");
+  m.def("swap_out_staged(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, Tensor staging, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None) -> ()");
+  m.def("swap_in_staged(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, Tensor staging, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None) -> ()");
   m.def("swap_in_relayout(Tensor layerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None) -> ()");
   m.def("swap_out_relayout(Tensor layerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None) -> ()");
   m.def("device_status() -> int");
@@ -357,6 +395,8 @@ TORCH_LIBRARY_IMPL(pcie_through, CUDA, m) {
   m.impl("swap_out", TORCH_FN(pciethrough::swap_out));
   m.impl("swap_in", TORCH_FN(pciethrough::swap_in));
   m.impl("paged_gather", TORCH_FN(pciethrough::paged_gather));
+  m.impl("swap_out_staged", TORCH_FN(pciethrough::swap_out_staged));
+  m.impl("swap_in_staged", TORCH_FN(pciethrough::swap_in_staged));
   m.impl("swap_in_relayout", TORCH_FN(pciethrough::swap_in_relayout));
   m.impl("swap_out_relayout", TORCH_FN(pciethrough::swap_out_relayout));
 }

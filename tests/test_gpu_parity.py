@@ -417,3 +417,46 @@ def test_relayout_swap_single_block_equals_multi_layer_block_transfer(hfk, cuda_
         assert hfk.device_status() == hfk.HFK_DEV_BAD_DEVICE_BLOCK_ID
     finally:
         pool.close()
+
+
+# ------------------------------------------------------ staged copy-engine mover ---
+@pytest.mark.parametrize("staging_slots", [1, 3, 64])
+def test_staged_swap_matches_oracle(hfk, cuda_device, staging_slots):
+    layers, blocks, chunk, nslots, n = 3, 40, (16, 2, 64), 50, 17
+    case = SwapCase(hfk, cuda_device, layers, blocks, chunk, torch.bfloat16, nslots, seed=21)
+    try:
+        slot_bytes = layers * 2 * 16 * 2 * 64 * 2
+        staging = torch.empty(staging_slots * slot_bytes, dtype=torch.uint8, device=cuda_device)
+        ids = o.distinct_ids(n, blocks, 1)
+        rest = [x for x in o.distinct_ids(nslots, nslots, 2).tolist() if not 5 <= x <= 10][:n - 6]
+        slots = torch.tensor(list(range(5, 11)) + rest)                   # distinct, starts with a consecutive run
+        ids_d = ids.to(cuda_device)
+        d = case.desc(ids_d, ids_d)
+        lib = hfk.lib()
+        hfk.check(lib.hfk_swap_staged(C.byref(d), slots.data_ptr(), case.pool.ptr, staging.data_ptr(), staging.numel(),
+                                      1, 0, stream_handle()), "staged out")
+        torch.cuda.synchronize()
+        o.swap_out(case.cpu_k, case.cpu_v, case.cpu_pool, ids, slots)
+        assert same_bytes(case.pool_view, case.cpu_pool)
+        ids2 = o.distinct_ids(n, blocks, 3)
+        ids2_d = ids2.to(cuda_device)
+        d = case.desc(ids2_d, ids2_d)
+        hfk.check(lib.hfk_swap_staged(C.byref(d), slots.data_ptr(), case.pool.ptr, staging.data_ptr(), staging.numel(),
+                                      0, 8, stream_handle()), "staged in")
+        torch.cuda.synchronize()
+        o.swap_in(case.cpu_k, case.cpu_v, case.cpu_pool, ids2, slots)
+        for g, c in zip(case.gpu_k + case.gpu_v, case.cpu_k + case.cpu_v):
+            assert same_bytes(g, c)
+        assert hfk.device_status() == 0
+        # errors: a staging buffer below one slot, a slot id out of range (checked on the host), a layer-major pool
+        assert lib.hfk_swap_staged(C.byref(d), slots.data_ptr(), case.pool.ptr, staging.data_ptr(), slot_bytes - 16,
+                                   0, 0, stream_handle()) == hfk.HFK_ERR_TOO_LARGE
+        bad = slots.clone()
+        bad[3] = nslots
+        assert lib.hfk_swap_staged(C.byref(d), bad.data_ptr(), case.pool.ptr, staging.data_ptr(), staging.numel(),
+                                   0, 0, stream_handle()) == hfk.HFK_ERR_INVALID_ARG
+        d.host_kv_stride = 4096 * 16
+        assert lib.hfk_swap_staged(C.byref(d), slots.data_ptr(), case.pool.ptr, staging.data_ptr(), staging.numel(),
+                                   0, 0, stream_handle()) == hfk.HFK_ERR_UNSUPPORTED
+    finally:
+        case.close()

@@ -140,6 +140,15 @@ def test_connector_swap_and_gather_round_trip(ops, cuda_device, mover):
     k_out, v_out = cache.paged_gather(tables, torch.tensor(g.seq_lens), mover=mover)
     ko, vo = o.paged_gather(cpu_k, cpu_v, tables, torch.tensor(g.seq_lens), g.block_size)
     assert torch.equal(u8(k_out.cpu()), u8(ko)) and torch.equal(u8(v_out.cpu()), u8(vo))
+    # staged mover (packing kernel + one copy-engine transfer per slot)
+    cache.swap_out_staged(back, slots, staging_bytes=1 << 20)
+    cache.swap_in_staged(ids, slots, staging_bytes=1 << 20)
+    o.swap_out(cpu_k, cpu_v, ref_pool, back, slots)
+    o.swap_in(cpu_k, cpu_v, ref_pool, ids, slots)
+    torch.cuda.synchronize()
+    assert torch.equal(u8(cache.host_pool), u8(ref_pool))
+    for dt, ct in zip(cache.k_caches + cache.v_caches, cpu_k + cpu_v):
+        assert torch.equal(u8(dt.cpu()), u8(ct))
     # copy-engine twins
     cache.swap_out_copy_engine(ids, slots)
     torch.cuda.synchronize()
