@@ -606,6 +606,7 @@ def main() -> None:
     from heterofusedkernels_b200.connector import PagedKVCache
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    pkg.load_ops()
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     ctx.init("nccl", device)
