@@ -372,14 +372,14 @@ def bench_block_transfer(device, args, pkg) -> dict:
         staging = [torch.empty((B, L, H, D), dtype=torch.int8, device=device) for _ in range(2)]
         row = {"block": [B, L, H, D], "bytes_per_op": nbytes}
         for fused in (False, True):
-            for aiv_label, aiv in (("default", None), ("aiv4", 4)):
+            for aiv_label, aiv, n_streams in (("default", None, 2), ("aiv4", 4, 2), ("one_stream", None, 1)):
                 best = 0.0
                 for rep in range(3):
                     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                            for _ in range(n_ops)]
                     torch.cuda.synchronize()
                     for i in range(n_ops):
-                        with torch.cuda.stream(streams[i % 2]):
+                        with torch.cuda.stream(streams[i % n_streams]):
                             evs[i][0].record()
                             if fused:
                                 op.fused_memcpy_multi_layer_block_transfer(ptr_tabs[i], pool[i], staging[i % 2], aiv)

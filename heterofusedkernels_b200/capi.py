@@ -103,6 +103,7 @@ PROTOTYPES = {
     "hfk_last_error_message": (C.c_char_p, []),
     "hfk_version": (C.c_char_p, []),
     "hfk_device_status": (C.c_int, [C.POINTER(C.c_uint), C.c_void_p]),
+    "hfk_selftest_wait_timeout": (C.c_int, [C.c_uint, C.c_void_p]),
     "hfk_set_bulk_geometry": (C.c_int, [C.c_int, C.c_int]),
     "hfk_set_bulk_lag": (C.c_int, [C.c_int]),
     "hfk_set_vector_geometry": (C.c_int, [C.c_int, C.c_int]),

@@ -88,13 +88,25 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Waits for the phase with the given parity, for at most kWaitLimitNs.  Returns
 // false when it gave up; the caller raises HFK_DEV_WAIT_TIMEOUT and leaves.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
+                                                  uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   while (!mbar_try_wait(bar, parity)) {
-    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    if (global_timer_ns() - t0 > limit_ns) return false;
   }
   return true;
+}
+
+// Self-test of the bounded wait: one warp waits on a barrier that nothing ever completes, gives
+// up after limit_ns, raises HFK_DEV_WAIT_TIMEOUT and returns — the context stays usable.
+__global__ void __launch_bounds__(32) wait_timeout_selftest_kernel(uint64_t limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    if (!mbar_wait_bounded(&bar, 0, limit_ns)) raise_status(HFK_DEV_WAIT_TIMEOUT);
+  }
 }
 // global -> this CTA's shared memory, completion counted in bytes on `bar`.
 __device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes,
@@ -142,7 +154,6 @@ struct CopyDesc {
 // kLag (template parameter of the pump) = how many of the most recent stores may still be
 // reading their stage when the next load is issued; the remaining n_stages - kLag stages hold
 // loads in flight.  Compiled values:
-constexpr int kPumpLagDefault = 2;
 constexpr int kPumpLagMax = 8;
 
 struct PumpSmem {

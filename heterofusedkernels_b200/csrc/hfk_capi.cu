@@ -205,9 +205,7 @@ static int validate_gather(const hfk_paged_gather_desc *d) {
   if (d->layers <= 0 || d->num_seqs < 0 || d->block_size <= 0 || d->token_bytes <= 0 ||
       d->max_blocks_per_seq < 0 || d->num_device_blocks <= 0 || d->total_tokens < 0)
     return fail(HFK_ERR_INVALID_ARG, "paged_gather: non-positive geometry");
-  if (d->num_seqs > HFK_MAX_SEQS)
-    return fail(HFK_ERR_TOO_LARGE, "paged_gather: %lld sequences > HFK_MAX_SEQS=%d",
-                (long long)d->num_seqs, HFK_MAX_SEQS);
+  if (d->num_seqs >= (int64_t)1 << 30) return fail(HFK_ERR_TOO_LARGE, "paged_gather: too many sequences");
   if (d->num_seqs > 0 && (!d->block_tables || !d->seq_lens))
     return fail(HFK_ERR_INVALID_ARG, "paged_gather: null block table or sequence lengths");
   if (d->block_table_stride < d->max_blocks_per_seq)
@@ -235,6 +233,9 @@ static cudaError_t launch_gather_vector(const GatherArgs &a, int ctas, cudaStrea
   return cudaGetLastError();
 }
 
+static int gather_launch(const GatherArgs &a, const hfk_paged_gather_desc *d, int mover, int ctas,
+                         cudaStream_t stream);
+
 static int gather_impl(const hfk_paged_gather_desc *d, int mover, int ctas, cudaStream_t stream) {
   int rc = validate_gather(d);
   if (rc != HFK_OK) return rc;
@@ -249,7 +250,8 @@ static int gather_impl(const hfk_paged_gather_desc *d, int mover, int ctas, cuda
   a.seq_lens = d->seq_lens;
   a.ids_are_int64 = d->ids_are_int64;
   a.layers = d->layers;
-  a.num_seqs = (int)d->num_seqs;
+  a.num_seqs = 0;
+  a.seq_offset = 0;
   a.max_blocks_per_seq = d->max_blocks_per_seq;
   a.block_table_stride = d->block_table_stride;
   a.block_size = d->block_size;
@@ -258,6 +260,19 @@ static int gather_impl(const hfk_paged_gather_desc *d, int mover, int ctas, cuda
   a.num_device_blocks = d->num_device_blocks;
   a.total_tokens = d->total_tokens;
   if (mover == HFK_MOVER_AUTO) mover = kDefaultMoverGather;
+  // The per-CTA walk tables hold HFK_MAX_SEQS sequences; larger batches go out as several launches,
+  // each of which derives its output offset from the lengths of the sequences before it.
+  for (int64_t first = 0; first < d->num_seqs; first += HFK_MAX_SEQS) {
+    a.seq_offset = (int)first;
+    a.num_seqs = (int)std::min<int64_t>(HFK_MAX_SEQS, d->num_seqs - first);
+    rc = gather_launch(a, d, mover, ctas, stream);
+    if (rc != HFK_OK) return rc;
+  }
+  return HFK_OK;
+}
+
+static int gather_launch(const GatherArgs &a, const hfk_paged_gather_desc *d, int mover, int ctas,
+                         cudaStream_t stream) {
   if (mover == HFK_MOVER_VECTOR) {
     if (ctas <= 0) ctas = sm_count() * kGatherVectorCtasPerSm;
     const int th = g_vec_threads.load(), un = g_vec_unroll.load();
@@ -521,6 +536,15 @@ int hfk_device_status(unsigned int *status_bits, hfk_stream_t stream) {
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyToSymbol(status)");
   }
   *status_bits = v;
+  return HFK_OK;
+}
+
+int hfk_selftest_wait_timeout(unsigned int limit_us, hfk_stream_t stream) {
+  if (limit_us == 0 || limit_us > 1000000u)
+    return fail(HFK_ERR_INVALID_ARG, "selftest_wait_timeout: limit must be 1..1000000 microseconds");
+  wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>((uint64_t)limit_us * 1000ull);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "wait_timeout_selftest_kernel launch");
   return HFK_OK;
 }
 

@@ -25,7 +25,8 @@ struct GatherArgs {
   const void *seq_lens;
   int ids_are_int64;
   int layers;
-  int num_seqs;
+  int num_seqs;     // sequences handled by this launch (<= HFK_MAX_SEQS)
+  int seq_offset;   // index of the first of them in block_tables / seq_lens
   int64_t max_blocks_per_seq;
   int64_t block_table_stride;
   int64_t block_size;
@@ -47,11 +48,20 @@ __device__ __forceinline__ void build_walk_tables(const GatherArgs &a, GatherTab
   if (threadIdx.x >= 32) return;
   const int lane = threadIdx.x;
   const int64_t cap = a.max_blocks_per_seq * a.block_size;
+  // output offset of this launch's first sequence: the (clamped) lengths of all earlier ones
   int64_t carry_tok = 0;
+  for (int base = 0; base < a.seq_offset; base += 32) {
+    const int s = base + lane;
+    int64_t len = s < a.seq_offset ? load_id(a.seq_lens, a.ids_are_int64, s) : 0;
+    len = len < 0 ? 0 : (len > cap ? cap : len);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) len += __shfl_xor_sync(0xffffffffu, len, d);
+    carry_tok += len;
+  }
   int32_t carry_blk = 0;
   for (int base = 0; base < a.num_seqs; base += 32) {
     const int s = base + lane;
-    int64_t len = s < a.num_seqs ? load_id(a.seq_lens, a.ids_are_int64, s) : 0;
+    int64_t len = s < a.num_seqs ? load_id(a.seq_lens, a.ids_are_int64, a.seq_offset + s) : 0;
     if (len < 0 || len > cap) {
       raise_status(HFK_DEV_BAD_SEQ_LEN);
       len = len < 0 ? 0 : cap;
@@ -101,7 +111,8 @@ __device__ __forceinline__ PageCopy locate_page(const GatherArgs &a, const Gathe
   const int64_t j = p - t->cu_blk[s];
   const int64_t len = t->cu_tok[s + 1] - t->cu_tok[s];
   const int64_t ntok = min(a.block_size, len - j * a.block_size);
-  const int64_t blk = load_id(a.block_tables, a.ids_are_int64, (int64_t)s * a.block_table_stride + j);
+  const int64_t blk =
+      load_id(a.block_tables, a.ids_are_int64, (int64_t)(a.seq_offset + s) * a.block_table_stride + j);
   const int64_t tok0 = t->cu_tok[s] + j * a.block_size;
   PageCopy c;
   c.src_off = 0; c.dst_off = 0; c.bytes = 0;

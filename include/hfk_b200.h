@@ -66,6 +66,11 @@ const char *hfk_version(void);
  * Synchronises `stream` first, so it is not for the hot loop. */
 int hfk_device_status(unsigned int *status_bits, hfk_stream_t stream);
 
+/* Self-test of the kernels' bounded waits: a one-warp kernel waits on a barrier that nothing
+ * completes, gives up after limit_us microseconds (1..1000000), sets HFK_DEV_WAIT_TIMEOUT in the
+ * status word and returns normally.  The data-path kernels use the same wait with a 2 s limit. */
+int hfk_selftest_wait_timeout(unsigned int limit_us, hfk_stream_t stream);
+
 /* Tuning knobs, process-wide, meant for benchmarking.  Ring of the bulk mover:
  * stage_bytes (multiple of 128) x n_stages of shared memory per CTA; vector
  * mover: threads per CTA x 16-byte loads in flight per thread (only a few
@@ -316,7 +321,7 @@ typedef struct hfk_paged_gather_desc {
   const void *seq_lens;
   int ids_are_int64;
   int layers;
-  int64_t num_seqs;           /* <= HFK_MAX_SEQS */
+  int64_t num_seqs;           /* batches above HFK_MAX_SEQS are split into several launches */
   int64_t max_blocks_per_seq;
   int64_t block_table_stride;
   int64_t block_size;         /* tokens per block */

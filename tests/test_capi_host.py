@@ -85,6 +85,35 @@ def test_copy_engine_rejects_out_of_range_ids_on_the_host(hfk):
     assert "out of range" in hfk.last_error()
 
 
+def test_staged_and_relayout_validation_errors(hfk):
+    lib = hfk.lib()
+    d, buf = _swap_desc(hfk)
+    stg = 0x40000
+    assert lib.hfk_swap_staged(C.byref(d), buf.data_ptr(), 0x10000, None, 1 << 20, 1, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    assert lib.hfk_swap_staged(C.byref(d), buf.data_ptr(), 0x10000, stg, 4096, 1, 0, None) == hfk.HFK_ERR_TOO_LARGE
+    assert lib.hfk_swap_staged(C.byref(d), None, 0x10000, stg, 1 << 20, 1, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    buf[:4] = torch.tensor([0, 1, 8, 2])                     # slot 8 of 8: rejected on the host
+    assert lib.hfk_swap_staged(C.byref(d), buf.data_ptr(), 0x10000, stg, 1 << 20, 0, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    d2, buf2 = _swap_desc(hfk, host_layer_stride=16384, host_slot_stride=8192)   # layer-major pool
+    assert lib.hfk_swap_staged(C.byref(d2), buf2.data_ptr(), 0x10000, stg, 1 << 20, 0, 0, None) == hfk.HFK_ERR_UNSUPPORTED
+    r = hfk.RelayoutDesc()
+    r.layer_ptrs = r.device_block_ids = r.host_slot_ids = buf.data_ptr()
+    r.host_pool = 0x10000
+    r.ids_are_int64, r.layers, r.n_blocks = 1, 2, 3
+    r.block_size, r.heads, r.head_bytes = 16, 2, 64
+    r.device_block_stride, r.host_slot_stride = 2048, 4096
+    r.num_device_blocks = r.num_host_slots = 8
+    for field, value, code in (("head_bytes", 24, "HFK_ERR_ALIGNMENT"), ("device_block_stride", 1024, "HFK_ERR_INVALID_ARG"),
+                               ("host_slot_stride", 2048, "HFK_ERR_INVALID_ARG"), ("layers", 0, "HFK_ERR_INVALID_ARG"),
+                               ("host_pool", 0, "HFK_ERR_INVALID_ARG")):
+        old = getattr(r, field)
+        setattr(r, field, value)
+        assert lib.hfk_swap_relayout(C.byref(r), 0, 0, None) == getattr(hfk, code), field
+        setattr(r, field, old)
+    assert lib.hfk_swap_relayout(None, 1, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    assert lib.hfk_set_bulk_lag(9) == hfk.HFK_ERR_INVALID_ARG and lib.hfk_set_bulk_lag(0) == hfk.HFK_OK
+
+
 def _gather_desc(hfk, **over):
     d = hfk.PagedGatherDesc()
     buf = torch.zeros(64, dtype=torch.int64)
@@ -103,7 +132,7 @@ def _gather_desc(hfk, **over):
 
 @pytest.mark.parametrize("over,code", [
     (dict(k_out=0), "HFK_ERR_INVALID_ARG"), (dict(token_bytes=250), "HFK_ERR_ALIGNMENT"),
-    (dict(num_seqs=5000), "HFK_ERR_TOO_LARGE"), (dict(block_table_stride=2), "HFK_ERR_INVALID_ARG"),
+    (dict(num_seqs=2**30, max_blocks_per_seq=1, block_table_stride=1), "HFK_ERR_TOO_LARGE"), (dict(block_table_stride=2), "HFK_ERR_INVALID_ARG"),
     (dict(device_block_stride=2048), "HFK_ERR_INVALID_ARG"), (dict(v_out=0x30004), "HFK_ERR_ALIGNMENT"),
     (dict(out_layer_stride=256), "HFK_ERR_INVALID_ARG"), (dict(block_size=0), "HFK_ERR_INVALID_ARG")])
 def test_paged_gather_validation_errors(hfk, over, code):

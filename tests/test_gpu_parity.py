@@ -229,6 +229,7 @@ GATHER_CASES = [
     (2, 40, 16, (4, 128), o.FP8, [250, 1, 64], torch.int64),                       # fp8
     (1, 30, 20, (8, 128), torch.float16, [41, 400], torch.int64),                  # 40 KiB pages: > one ring stage
     (1, 600, 1, (2, 8), torch.int8, list(range(0, 33)), torch.int64),              # block_size 1, 33 sequences
+    (2, 6000, 2, (1, 8), torch.float16, [(7 * i) % 5 for i in range(2500)], torch.int32),  # more sequences than one launch's walk table
 ]
 
 
@@ -460,3 +461,21 @@ def test_staged_swap_matches_oracle(hfk, cuda_device, staging_slots):
                                    0, 0, stream_handle()) == hfk.HFK_ERR_UNSUPPORTED
     finally:
         case.close()
+
+
+def test_bounded_wait_gives_up_and_reports_instead_of_hanging(hfk, cuda_device):
+    """A wait on a barrier nobody completes runs out after its limit; the kernel returns, the status
+    word says so and the context keeps working."""
+    import time
+
+    lib = hfk.lib()
+    assert hfk.device_status() == 0
+    t0 = time.perf_counter()
+    hfk.check(lib.hfk_selftest_wait_timeout(20000, stream_handle()), "selftest")   # 20 ms
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert 0.015 < dt < 1.0
+    assert hfk.device_status() == hfk.HFK_DEV_WAIT_TIMEOUT
+    x = torch.arange(8, device=cuda_device)
+    assert int(x.sum()) == 28 and hfk.device_status() == 0
+    assert lib.hfk_selftest_wait_timeout(0, stream_handle()) == hfk.HFK_ERR_INVALID_ARG
