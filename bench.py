@@ -763,6 +763,17 @@ def main() -> None:
                 "swap_out": {"achieved": out_gbs, "peak": pcie["d2h"], "frac": out_gbs / pcie["d2h"]},
                 "swap_in": {"achieved": in_gbs, "peak": pcie["h2d"], "frac": in_gbs / pcie["h2d"]},
                 "nominal_gen5_x16": 63.0, "algorithmic_bytes_per_launch": g.swap_bytes}
+    if pcie_conc is not None:
+        # N > 1: what the host gives N links at once is the meaningful denominator
+        agg_out = sum(r[1] for r in per_rank)
+        agg_in = sum(r[2] for r in per_rank)
+        conc_d2h = sum(r[1] for r in pcie_conc)
+        conc_h2d = sum(r[0] for r in pcie_conc)
+        roofline["all_ranks_concurrent"] = {
+            "swap_out_aggregate": agg_out, "memcpy_d2h_aggregate": conc_d2h, "frac_out": agg_out / conc_d2h,
+            "swap_in_aggregate": agg_in, "memcpy_h2d_aggregate": conc_h2d, "frac_in": agg_in / conc_h2d,
+            "note": "cudaMemcpyAsync with every rank copying at once (8 x 1 GiB per direction after a barrier); "
+                    "roofline.peak above is one link alone"}
     line = {"metric": "kv_swap_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "u8", "data": "synthetic", "config": config,

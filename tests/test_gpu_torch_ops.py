@@ -203,3 +203,50 @@ def test_relayout_swap_ops(ops, cuda_device):
     assert torch.equal(u8(pool), u8(cpu_pool))
     for g, c in zip(gpu_dev, cpu_dev):
         assert torch.equal(u8(g.cpu()), u8(c))
+
+
+def test_swap_and_gather_ops_replay_from_a_cuda_graph(ops, cuda_device):
+    """The ops neither allocate nor synchronise, so a serving engine can capture them; the reference
+    leaves graph capture open (multi_layer_block_transfer_torch.cpp:57)."""
+    from heterofusedkernels_b200.connector import PagedKVCache
+
+    g = o.CONFIGS["tiny"]
+    cache = PagedKVCache(g.layers, g.num_blocks, g.block_size, g.kv_heads, g.head_dim, g.dtype, cuda_device,
+                         host_slots=g.host_slots)
+    shape = (g.num_blocks, g.block_size, g.kv_heads, g.head_dim)
+    ids = o.distinct_ids(8, 64, 1).to(cuda_device)
+    slots = o.distinct_ids(8, 128, 2).to(cuda_device)
+    back = o.distinct_ids(8, 64, 3).to(cuda_device)
+    tables = o.block_tables_for(g.seq_lens, g.block_size, g.num_blocks, seed=4).to(cuda_device)
+    lens = torch.tensor(g.seq_lens, device=cuda_device)
+    k_out = torch.zeros((g.layers, sum(g.seq_lens), g.kv_heads, g.head_dim), dtype=g.dtype, device=cuda_device)
+    v_out = torch.zeros_like(k_out)
+
+    def step():
+        cache.swap_out(ids, slots)
+        cache.swap_in(back, slots)
+        cache.paged_gather(tables, lens, k_out, v_out)
+
+    side = torch.cuda.Stream(cuda_device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        step()                                   # warm-up outside the capture
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+    for rep in range(2):                         # new cache contents, same graph
+        cpu_k = [o.random_kv_bytes(shape, g.dtype, 100 * rep + 2 * l) for l in range(g.layers)]
+        cpu_v = [o.random_kv_bytes(shape, g.dtype, 100 * rep + 2 * l + 1) for l in range(g.layers)]
+        for d, s in zip(cache.k_caches + cache.v_caches, cpu_k + cpu_v):
+            d.copy_(s)
+        cache.host_pool.zero_()
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        ref_pool = torch.zeros_like(cache.host_pool)
+        o.swap_out(cpu_k, cpu_v, ref_pool, ids.cpu(), slots.cpu())
+        o.swap_in(cpu_k, cpu_v, ref_pool, back.cpu(), slots.cpu())
+        ko, vo = o.paged_gather(cpu_k, cpu_v, tables.cpu(), lens.cpu(), g.block_size)
+        assert torch.equal(u8(cache.host_pool), u8(ref_pool))
+        assert torch.equal(u8(k_out.cpu()), u8(ko)) and torch.equal(u8(v_out.cpu()), u8(vo))
+    assert cache.status() == 0
