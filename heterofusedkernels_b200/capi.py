@@ -107,6 +107,7 @@ PROTOTYPES = {
     "hfk_set_bulk_geometry": (C.c_int, [C.c_int, C.c_int]),
     "hfk_set_bulk_lag": (C.c_int, [C.c_int]),
     "hfk_set_vector_geometry": (C.c_int, [C.c_int, C.c_int]),
+    "hfk_set_gather_tuning": (C.c_int, [C.c_int, C.c_int]),
     "hfk_register_ptr": (C.c_void_p, [C.c_void_p, C.c_size_t]),
     "hfk_unregister_ptr": (C.c_int, [C.c_void_p]),
     "hfk_get_device_ptr": (C.c_size_t, [C.c_size_t]),

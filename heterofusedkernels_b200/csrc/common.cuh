@@ -123,6 +123,26 @@ __device__ __forceinline__ void bulk_store(void *gdst, const void *smem_src, uin
                "r"(smem_addr(smem_src)), "r"(bytes)
                : "memory");
 }
+// The same two copies with an L2 eviction-priority hint (policy from make_evict_first_policy()).
+__device__ __forceinline__ uint64_t make_evict_first_policy() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void bulk_load_hint(void *smem_dst, const void *gsrc, uint32_t bytes,
+                                               uint64_t *bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+          smem_addr(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_store_hint(void *gdst, const void *smem_src, uint32_t bytes,
+                                                uint64_t policy) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;" ::"l"(gdst),
+               "r"(smem_addr(smem_src)), "r"(bytes), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -165,8 +185,10 @@ struct PumpSmem {
 template <int kPumpLag, typename MakeDesc>
 __device__ __forceinline__ void run_pump(PumpSmem *ps, unsigned char *stages, int stage_bytes,
                                          int n_stages, int64_t total, uint32_t &seq,
-                                         MakeDesc make_desc) {
+                                         MakeDesc make_desc, int hints = 0) {
+  // hints: bit 0 = loads carry an L2 evict-first policy, bit 1 = stores do
   const int lane = threadIdx.x & 31;
+  const uint64_t policy = hints ? make_evict_first_policy() : 0;
   const int in_flight = n_stages - kPumpLag;  // loads kept in flight
   int64_t issued = 0, done = 0;
   bool ok = true;
@@ -185,7 +207,10 @@ __device__ __forceinline__ void run_pump(PumpSmem *ps, unsigned char *stages, in
     if (lane == 0) {
       if (d.bytes != 0) {
         mbar_expect_tx(&ps->full[slot], d.bytes);
-        bulk_load(stages + (size_t)slot * stage_bytes, d.src, d.bytes, &ps->full[slot]);
+        if (hints & 1)
+          bulk_load_hint(stages + (size_t)slot * stage_bytes, d.src, d.bytes, &ps->full[slot], policy);
+        else
+          bulk_load(stages + (size_t)slot * stage_bytes, d.src, d.bytes, &ps->full[slot]);
       } else {
         mbar_arrive(&ps->full[slot]);  // a skipped unit still completes its phase
       }
@@ -210,7 +235,10 @@ __device__ __forceinline__ void run_pump(PumpSmem *ps, unsigned char *stages, in
         ok = mbar_wait_bounded(&ps->full[slot], parity);
         if (ok) {
           fence_async_proxy();
-          bulk_store(d.dst, stages + (size_t)slot * stage_bytes, d.bytes);
+          if (hints & 2)
+            bulk_store_hint(d.dst, stages + (size_t)slot * stage_bytes, d.bytes, policy);
+          else
+            bulk_store(d.dst, stages + (size_t)slot * stage_bytes, d.bytes);
         }
       }
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;

@@ -43,6 +43,7 @@ int cuda_fail(cudaError_t e, const char *what) {
 
 // ---- tuning state ----------------------------------------------------------
 std::atomic<int> g_stage_bytes{0}, g_n_stages{0}, g_bulk_lag{0}, g_vec_threads{0}, g_vec_unroll{0};
+std::atomic<int> g_gather_hints{-1}, g_gather_blocked{-1};
 
 constexpr int kMaxDynSmem = 227 * 1024;
 
@@ -252,6 +253,8 @@ static int gather_impl(const hfk_paged_gather_desc *d, int mover, int ctas, cuda
   a.layers = d->layers;
   a.num_seqs = 0;
   a.seq_offset = 0;
+  a.hints = g_gather_hints.load() >= 0 ? g_gather_hints.load() : kGatherHints;
+  a.blocked = g_gather_blocked.load() >= 0 ? g_gather_blocked.load() : kGatherBlocked;
   a.max_blocks_per_seq = d->max_blocks_per_seq;
   a.block_table_stride = d->block_table_stride;
   a.block_size = d->block_size;
@@ -545,6 +548,14 @@ int hfk_selftest_wait_timeout(unsigned int limit_us, hfk_stream_t stream) {
   wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>((uint64_t)limit_us * 1000ull);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "wait_timeout_selftest_kernel launch");
+  return HFK_OK;
+}
+
+int hfk_set_gather_tuning(int l2_hints, int blocked) {
+  if (l2_hints < -1 || l2_hints > 3 || blocked < -1 || blocked > 1)
+    return fail(HFK_ERR_INVALID_ARG, "gather tuning: l2_hints -1..3, blocked -1..1");
+  g_gather_hints = l2_hints;
+  g_gather_blocked = blocked;
   return HFK_OK;
 }
 

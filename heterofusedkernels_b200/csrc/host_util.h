@@ -27,6 +27,7 @@ constexpr int kDefaultSwapCtasVector = 16;
 constexpr int kDefaultSwapCtasBulk = 4;
 constexpr int kSwapStageBytes = 16384, kSwapStages = 8, kSwapLag = 2;
 constexpr int kGatherStageBytes = 32768, kGatherStages = 4, kGatherLag = 2;
+constexpr int kGatherHints = 3, kGatherBlocked = 0;  // bulk gather: evict-first on loads and stores (+0.5 %), interleaved units
 constexpr int kGatherVectorCtasPerSm = 2;  // vector mover: 256 threads x 8 loads, 2 CTAs per SM
 constexpr int kDefaultRowGatherCtas = 32;
 constexpr int kDefaultTransferCtas = 32;

@@ -34,6 +34,8 @@ struct GatherArgs {
   int64_t device_block_stride;
   int64_t num_device_blocks;
   int64_t total_tokens;
+  int hints;    // L2 hints of the bulk mover (run_pump)
+  int blocked;  // 0: CTA c takes units c, c+grid, ...; 1: CTA c takes one contiguous run of units
 };
 
 // Per-CTA shared-memory walk tables: exclusive prefix sums over the sequences of
@@ -174,10 +176,16 @@ __global__ void __launch_bounds__(32) paged_gather_bulk_kernel(GatherArgs a, int
   const int64_t page_bytes = a.block_size * a.token_bytes;
   const int pieces = (int)((page_bytes + stage_bytes - 1) / stage_bytes);
   const int64_t units = pages * 2 * a.layers * pieces;
-  const int64_t mine = units > blockIdx.x ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  int64_t mine = units > blockIdx.x ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  int64_t first_unit = 0;
+  if (a.blocked) {
+    const int64_t per = (units + gridDim.x - 1) / gridDim.x;
+    first_unit = per * blockIdx.x;
+    mine = first_unit < units ? min(per, units - first_unit) : 0;
+  }
   uint32_t seq = 0;
   run_pump<kLag>(ps, stages, stage_bytes, n_stages, mine, seq, [&](int64_t k) {
-    const int64_t g = blockIdx.x + k * (int64_t)gridDim.x;
+    const int64_t g = a.blocked ? first_unit + k : blockIdx.x + k * (int64_t)gridDim.x;
     const int64_t w = g / pieces;
     const int piece = (int)(g - w * pieces);
     const int lk = (int)(w / pages);
@@ -193,7 +201,7 @@ __global__ void __launch_bounds__(32) paged_gather_bulk_kernel(GatherArgs a, int
     d.dst = (kv ? a.v_out : a.k_out) + (int64_t)l * a.out_layer_stride + c.dst_off + off;
     d.bytes = (uint32_t)min((int64_t)stage_bytes, c.bytes - off);
     return d;
-  });
+  }, a.hints);
 }
 
 }  // namespace hfk

@@ -80,6 +80,10 @@ int hfk_set_bulk_geometry(int stage_bytes, int n_stages);
  * loads in flight); compiled values 1, 2, 3, 4, 6, 8; 0 restores the default. */
 int hfk_set_bulk_lag(int lag);
 int hfk_set_vector_geometry(int threads, int unroll);
+/* Bulk paged gather: l2_hints bit 0 / bit 1 = loads / stores carry an L2 evict-first policy;
+ * blocked = 1 gives every CTA one contiguous run of pages instead of every grid-th page.
+ * -1 restores the default of either. */
+int hfk_set_gather_tuning(int l2_hints, int blocked);
 
 /* ======================================================================== *
  *  Host-memory registry and NUMA-local pinned allocation
