@@ -136,6 +136,8 @@ def cpu_baseline_swap(g, steps: int, warmup: int, budget_s: float = 25.0) -> dic
     pool shrunk to 2*n_swap blocks, so only the pools are smaller, not the bytes moved."""
     from oracle import kv_oracle as o
 
+    # launchers such as torchrun export OMP_NUM_THREADS=1; the CPU arm uses every host core
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     nb = 2 * g.n_swap
     shape = (nb, g.block_size, g.kv_heads, g.head_dim)
     store = torch.empty((2, g.layers) + shape[:1] + (g.block_bytes,), dtype=torch.uint8)
