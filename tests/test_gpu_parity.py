@@ -479,3 +479,70 @@ def test_bounded_wait_gives_up_and_reports_instead_of_hanging(hfk, cuda_device):
     x = torch.arange(8, device=cuda_device)
     assert int(x.sum()) == 28 and hfk.device_status() == 0
     assert lib.hfk_selftest_wait_timeout(0, stream_handle()) == hfk.HFK_ERR_INVALID_ARG
+
+
+# ------------------------------------------------------------- seeded random geometries ---
+def _rand_cases(n, seed):
+    g = torch.Generator().manual_seed(seed)
+
+    def r(lo, hi):
+        return int(torch.randint(lo, hi + 1, (1,), generator=g))
+
+    cases = []
+    for i in range(n):
+        layers, blocks = r(1, 5), r(4, 48)
+        tok_elems = 8 * r(1, 40)                      # fp16 elements per token row: 16-byte multiples
+        bs = r(1, 24)
+        cases.append(dict(i=i, layers=layers, blocks=blocks, bs=bs, tok=tok_elems, slots=r(blocks, 2 * blocks),
+                          n=r(1, blocks), mover=r(1, 2), ctas=r(1, 40), layout=("block_major", "layer_major")[r(0, 1)],
+                          idt=(torch.int64, torch.int32)[r(0, 1)], stage=(4096, 8192, 16384, 32768)[r(0, 3)],
+                          stages=r(3, 6)))
+    return cases
+
+
+@pytest.mark.parametrize("c", _rand_cases(24, 2024), ids=lambda c: f"case{c['i']}")
+def test_random_geometries_swap_gather_and_staged(hfk, cuda_device, c):
+    lib = hfk.lib()
+    assert lib.hfk_set_bulk_geometry(c["stage"], c["stages"]) == 0
+    case = SwapCase(hfk, cuda_device, c["layers"], c["blocks"], (c["bs"], 1, c["tok"]), torch.float16, c["slots"],
+                    seed=300 + c["i"], pool_layout=c["layout"])
+    try:
+        ids = o.distinct_ids(c["n"], c["blocks"], 1).to(c["idt"])
+        slots = o.distinct_ids(c["n"], c["slots"], 2).to(c["idt"])
+        run_swap(hfk, lib.hfk_swap_out, case.desc(ids.to(cuda_device), slots.to(cuda_device)), c["mover"], c["ctas"])
+        o.swap_out(case.cpu_k, case.cpu_v, case.cpu_pool, ids, slots)
+        assert same_bytes(case.pool_view, case.cpu_pool)
+        ids2 = o.distinct_ids(c["n"], c["blocks"], 3).to(c["idt"])
+        if c["layout"] == "block_major" and c["i"] % 2 == 0:   # staged mover needs a slot-contiguous pool
+            staging = torch.empty(3 * c["layers"] * 2 * c["bs"] * c["tok"] * 2 + 64, dtype=torch.uint8,
+                                  device=cuda_device)
+            d = case.desc(ids2.to(cuda_device), ids2.to(cuda_device))
+            hfk.check(lib.hfk_swap_staged(C.byref(d), slots.data_ptr(), case.pool.ptr, staging.data_ptr(),
+                                          staging.numel(), 0, c["ctas"], stream_handle()), "staged in")
+            torch.cuda.synchronize()
+        else:
+            run_swap(hfk, lib.hfk_swap_in, case.desc(ids2.to(cuda_device), slots.to(cuda_device)), c["mover"], c["ctas"])
+        o.swap_in(case.cpu_k, case.cpu_v, case.cpu_pool, ids2, slots)
+        for g, cc in zip(case.gpu_k + case.gpu_v, case.cpu_k + case.cpu_v):
+            assert same_bytes(g, cc)
+        # gather a ragged batch out of the same caches
+        gen = torch.Generator().manual_seed(c["i"])
+        lens, left = [], c["blocks"]
+        while left > 0 and len(lens) < 7:
+            nb = int(torch.randint(0, left + 1, (1,), generator=gen))
+            lens.append(max(0, nb * c["bs"] - int(torch.randint(0, c["bs"], (1,), generator=gen))) if nb else 0)
+            left -= nb
+        if sum(lens) == 0:
+            lens[0] = 1
+        tables = o.block_tables_for(lens, c["bs"], c["blocks"], seed=c["i"])
+        if tables.shape[1] == 0:
+            tables = torch.zeros((len(lens), 1), dtype=torch.int64)
+        lens_t = torch.tensor(lens)
+        k_out, v_out = run_gather(hfk, cuda_device, case.cpu_k, case.cpu_v, tables, lens_t, c["bs"], c["mover"],
+                                  c["idt"], ctas=c["ctas"])
+        ko, vo = o.paged_gather(case.cpu_k, case.cpu_v, tables, lens_t, c["bs"])
+        assert same_bytes(k_out, ko) and same_bytes(v_out, vo)
+        assert hfk.device_status() == 0
+    finally:
+        case.close()
+        lib.hfk_set_bulk_geometry(0, 0)
