@@ -86,7 +86,7 @@ def fill_random_bytes(t: torch.Tensor, seed: int) -> None:
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms in the background."""
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 100 ms in the background."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -95,7 +95,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
                  "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -522,8 +522,8 @@ def bench_overlap(g, device, args, pkg) -> dict:
     variants = []
     alone_all = []
     reps = 7
-    for kind, ctas in (("bulk", 2), ("bulk", 4), ("bulk", 8), ("vector", 4), ("vector", 8), ("vector", 16),
-                       ("copy_engine", 0)):
+    for kind, ctas in (("bulk", 2), ("bulk", 4), ("bulk", 8), ("bulk", 16), ("vector", 4), ("vector", 8),
+                       ("vector", 16), ("vector", 32), ("copy_engine", 0)):
         overlapped(kind, ctas)  # warm-up
         alone, runs = [], []
         for _ in range(reps if kind != "copy_engine" else 3):
@@ -796,7 +796,7 @@ def main() -> None:
                               "peak_source": hbm_src, "nominal": 8000.0}
         line["gather"] = gather
     if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline_swap(g, 3, 1)
+        line["cpu_baseline"] = cpu_baseline_swap(g, 10, 1)
     print(json.dumps(line), flush=True)
     ctx.close()
 
