@@ -574,6 +574,7 @@ def main() -> None:
     ap.add_argument("--no-gather", action="store_true")
     ap.add_argument("--gather-only", action="store_true", help="run only the paged-gather leg")
     ap.add_argument("--gather-seqs", type=int, default=64, help="sequences in the gather batch")
+    ap.add_argument("--gather-hints", type=int, default=-1, help="L2 hints of the bulk gather (-1 = library default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -609,6 +610,8 @@ def main() -> None:
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     pkg.load_ops()
+    if args.gather_hints >= 0:
+        pkg.capi.check(pkg.capi.lib().hfk_set_gather_tuning(args.gather_hints, -1), "hfk_set_gather_tuning")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     ctx.init("nccl", device)

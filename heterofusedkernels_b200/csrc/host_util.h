@@ -27,7 +27,10 @@ constexpr int kDefaultSwapCtasVector = 16;
 constexpr int kDefaultSwapCtasBulk = 4;
 constexpr int kSwapStageBytes = 16384, kSwapStages = 8, kSwapLag = 2;
 constexpr int kGatherStageBytes = 32768, kGatherStages = 4, kGatherLag = 2;
-constexpr int kGatherHints = 3, kGatherBlocked = 0;  // bulk gather: evict-first on loads and stores (+0.5 %), interleaved units
+constexpr int kGatherHints = 0, kGatherBlocked = 0;  // bulk gather: no L2 hints (see below), interleaved units
+// L2 evict-first hints on the gather's bulk copies measured 6.70 TB/s when an un-hinted launch had run
+// before in the same process and 6.50 TB/s in a fresh process (un-hinted: 6.67 TB/s either way), so
+// they stay off by default.
 constexpr int kGatherVectorCtasPerSm = 2;  // vector mover: 256 threads x 8 loads, 2 CTAs per SM
 constexpr int kDefaultRowGatherCtas = 32;
 constexpr int kDefaultTransferCtas = 32;
