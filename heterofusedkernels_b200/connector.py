@@ -147,7 +147,14 @@ class LayerwisePrefetcher:
 
     One single-layer view of the cache is made per layer (pointer tables of length 1),
     so each call moves only that layer's K and V.
+
+    Defaults: the vector mover with 16 CTAs per direction.  Measured next to a bf16 GEMM that fills
+    the device, its small CTAs share SMs with the GEMM's and both directions run at 41-44 GB/s with
+    the GEMM 2-5 % slower, while the bulk mover's CTAs (which need most of an SM's shared memory)
+    wait for free SMs and drop to about 18 GB/s.
     """
+    DEFAULT_AIV = 16
+    DEFAULT_MOVER = _pkg.capi.MOVER_VECTOR
 
     def __init__(self, cache: PagedKVCache):
         self.cache = cache
@@ -163,7 +170,8 @@ class LayerwisePrefetcher:
         c = self.cache
         with torch.cuda.stream(self.in_stream):
             torch.ops.pcie_through.swap_in(self.k_ptrs[layer], self.v_ptrs[layer], self.pools[layer],
-                                           device_block_ids, host_slot_ids, c.num_blocks, None, aiv, mover)
+                                           device_block_ids, host_slot_ids, c.num_blocks, None,
+                                           aiv or self.DEFAULT_AIV, mover or self.DEFAULT_MOVER)
             self.ready[layer].record()
         return self.ready[layer]
 
@@ -172,7 +180,8 @@ class LayerwisePrefetcher:
         c = self.cache
         with torch.cuda.stream(self.out_stream):
             torch.ops.pcie_through.swap_out(self.k_ptrs[layer], self.v_ptrs[layer], self.pools[layer],
-                                            device_block_ids, host_slot_ids, c.num_blocks, None, aiv, mover)
+                                            device_block_ids, host_slot_ids, c.num_blocks, None,
+                                            aiv or self.DEFAULT_AIV, mover or self.DEFAULT_MOVER)
 
     def wait(self, layer: int) -> None:
         torch.cuda.current_stream(self.cache.device).wait_event(self.ready[layer])
