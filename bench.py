@@ -466,7 +466,12 @@ def bench_overlap(g, device, args, pkg) -> dict:
         return overlapped(kind, ctas, with_gemm=False)
 
     def overlapped(kind, ctas, with_gemm=True):
-        mv = {"bulk": pkg.capi.MOVER_BULK, "vector": pkg.capi.MOVER_VECTOR}.get(kind)
+        mv = {"bulk": pkg.capi.MOVER_BULK, "bulk_small_ring": pkg.capi.MOVER_BULK,
+              "vector": pkg.capi.MOVER_VECTOR}.get(kind)
+        # "bulk_small_ring": 8 stages of 4 KiB (48 KB of shared memory with the id tile), so that the
+        # single-warp CTAs fit next to the GEMM's CTAs on an SM
+        pkg.capi.lib().hfk_set_bulk_geometry(4096 if kind == "bulk_small_ring" else 0,
+                                             8 if kind == "bulk_small_ring" else 0)
         ev_in = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L)]
         ev_out = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L)]
         torch.cuda.synchronize()
@@ -522,7 +527,8 @@ def bench_overlap(g, device, args, pkg) -> dict:
     variants = []
     alone_all = []
     reps = 7
-    for kind, ctas in (("bulk", 2), ("bulk", 4), ("bulk", 8), ("bulk", 16), ("vector", 4), ("vector", 8),
+    for kind, ctas in (("bulk", 2), ("bulk", 4), ("bulk", 8), ("bulk", 16), ("bulk_small_ring", 8),
+                       ("bulk_small_ring", 16), ("bulk_small_ring", 32), ("vector", 4), ("vector", 8),
                        ("vector", 16), ("vector", 32), ("copy_engine", 0)):
         overlapped(kind, ctas)  # warm-up
         alone, runs = [], []
@@ -538,11 +544,12 @@ def bench_overlap(g, device, args, pkg) -> dict:
                          "swap_in_gbs": statistics.median(r["in_gbs"] for r in runs),
                          "swap_out_gbs": statistics.median(r["out_gbs"] for r in runs),
                          "swap_in_gbs_no_gemm": solo["in_gbs"], "swap_out_gbs_no_gemm": solo["out_gbs"]})
+    pkg.capi.lib().hfk_set_bulk_geometry(0, 0)
     t_alone = statistics.median(alone_all)
     t_alone2 = statistics.median([gemm_pass() for _ in range(3)])
     clocks = sampler.stop()
     status = cache.status()
-    ok = [v for v in variants if v["mover"] != "copy_engine" and v["gemm_slowdown_pct"] < 10.0]
+    ok = [v for v in variants if v["mover"] in ("bulk", "vector") and v["gemm_slowdown_pct"] < 10.0]
     pick = max(ok or variants, key=lambda v: v["swap_in_gbs"] + v["swap_out_gbs"])
     return {"metric": "kv_swap_GBps_under_gemm_overlap", "value": (pick["swap_in_gbs"] + pick["swap_out_gbs"]) / 2,
             "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": 1, "ms_per_step": pick["gemm_ms_overlapped"],

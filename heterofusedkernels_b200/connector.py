@@ -149,9 +149,8 @@ class LayerwisePrefetcher:
     so each call moves only that layer's K and V.
 
     Defaults: the vector mover with 16 CTAs per direction.  Measured next to a bf16 GEMM that fills
-    the device, its small CTAs share SMs with the GEMM's and both directions run at 41-44 GB/s with
-    the GEMM 2-5 % slower, while the bulk mover's CTAs (which need most of an SM's shared memory)
-    wait for free SMs and drop to about 18 GB/s.
+    the device, both directions then run at 41-44 GB/s with the GEMM 2-5 % slower, while the bulk
+    mover with 8 or more single-warp CTAs drops to about 18 GB/s per direction.
     """
     DEFAULT_AIV = 16
     DEFAULT_MOVER = _pkg.capi.MOVER_VECTOR
