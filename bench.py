@@ -466,11 +466,10 @@ def bench_overlap(g, device, args, pkg) -> dict:
         return overlapped(kind, ctas, with_gemm=False)
 
     def overlapped(kind, ctas, with_gemm=True):
-        mv = {"bulk": pkg.capi.MOVER_BULK, "bulk_small_ring": pkg.capi.MOVER_BULK,
-              "bulk_tiny_ring": pkg.capi.MOVER_BULK, "vector": pkg.capi.MOVER_VECTOR}.get(kind)
-        # smaller rings so that the single-warp CTAs may fit next to the GEMM's CTAs on an SM:
-        # "bulk_small_ring" 8 x 4 KiB (48 KB of shared memory with the id tile), "bulk_tiny_ring" 4 x 2 KiB (26 KB)
-        ring = {"bulk_small_ring": (4096, 8), "bulk_tiny_ring": (2048, 4)}.get(kind, (0, 0))
+        # kind: "vector", "copy_engine", "bulk" (library ring) or "bulk@<stage bytes>x<stages>": smaller
+        # rings let the single-warp CTAs fit next to the GEMM's CTAs on an SM
+        mv = pkg.capi.MOVER_VECTOR if kind == "vector" else (pkg.capi.MOVER_BULK if kind.startswith("bulk") else None)
+        ring = tuple(int(x) for x in kind.split("@")[1].split("x")) if "@" in kind else (0, 0)
         pkg.capi.lib().hfk_set_bulk_geometry(*ring)
         ev_in = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L)]
         ev_out = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L)]
@@ -527,10 +526,10 @@ def bench_overlap(g, device, args, pkg) -> dict:
     variants = []
     alone_all = []
     reps = 7
-    for kind, ctas in (("bulk", 2), ("bulk", 4), ("bulk", 8), ("bulk", 16), ("bulk_small_ring", 8),
-                       ("bulk_small_ring", 16), ("bulk_small_ring", 32), ("bulk_tiny_ring", 16),
-                       ("bulk_tiny_ring", 32), ("bulk_tiny_ring", 64), ("vector", 4), ("vector", 8),
-                       ("vector", 16), ("vector", 32), ("copy_engine", 0)):
+    for kind, ctas in (("bulk", 2), ("bulk", 4), ("bulk", 8), ("bulk", 16), ("bulk@4096x8", 8), ("bulk@4096x8", 16),
+                       ("bulk@2048x4", 32), ("bulk@2048x8", 16), ("bulk@2048x8", 32), ("bulk@2048x8", 64),
+                       ("bulk@4096x4", 16), ("bulk@4096x4", 32), ("vector", 4), ("vector", 8), ("vector", 16),
+                       ("vector", 32), ("copy_engine", 0)):
         overlapped(kind, ctas)  # warm-up
         alone, runs = [], []
         for _ in range(reps if kind != "copy_engine" else 3):

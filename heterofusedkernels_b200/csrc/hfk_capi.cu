@@ -148,12 +148,14 @@ static SwapArgs to_args(const hfk_swap_desc *d) {
   return a;
 }
 
+static int swap_id_tile(int64_t n_blocks) { return (int)std::min<int64_t>(std::max<int64_t>(n_blocks, 1), kSwapIdTile); }
+
 template <bool kToHost, int kThreads, int kUnroll>
 static cudaError_t launch_swap_vector(const SwapArgs &a, int ctas, size_t smem, cudaStream_t s) {
   auto k = kv_swap_vector_kernel<kToHost, kThreads, kUnroll>;
   cudaError_t e = allow_smem(k, smem);
   if (e != cudaSuccess) return e;
-  k<<<ctas, kThreads, smem, s>>>(a);
+  k<<<ctas, kThreads, smem, s>>>(a, swap_id_tile(a.n_blocks));
   return cudaGetLastError();
 }
 
@@ -163,7 +165,7 @@ static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t s
   if (rc != HFK_OK) return rc;
   if (d->n_blocks == 0) return HFK_OK;
   const SwapArgs a = to_args(d);
-  const size_t tables = sizeof(SwapTables) + 2 * sizeof(void *) * (size_t)d->layers;
+  const size_t tables = swap_tables_bytes(swap_id_tile(d->n_blocks), d->layers);
   if (mover == HFK_MOVER_AUTO) mover = kToHost ? kDefaultMoverOut : kDefaultMoverIn;
   const int64_t items = d->n_blocks * 2 * d->layers;
   if (mover == HFK_MOVER_VECTOR) {
@@ -189,7 +191,7 @@ static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t s
       auto k = kv_swap_bulk_kernel<kToHost, decltype(lag)::value>;
       cudaError_t err = allow_smem(k, p.smem);
       if (err != cudaSuccess) return err;
-      k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
+      k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, swap_id_tile(a.n_blocks));
       return cudaGetLastError();
     });
     if (e != cudaSuccess) return cuda_fail(e, "kv_swap_bulk_kernel launch");
@@ -349,7 +351,7 @@ static int swap_staged_impl(const hfk_swap_desc *d, const void *slots_host, void
     k.host_slot_stride = slot_bytes;
     k.num_host_slots = n;
     const SwapArgs a = to_args(&k);
-    const size_t tables = sizeof(SwapTables) + 2 * sizeof(void *) * (size_t)d->layers;
+    const size_t tables = swap_tables_bytes(swap_id_tile(n), d->layers);
     const BulkPlan p = plan_bulk(d->block_bytes, tables, kGatherStageBytes, kGatherStages, kGatherLag);
     auto pack = [&](bool to_staging) -> cudaError_t {
       return launch_by_lag(p.lag, [&](auto lag) {
@@ -357,11 +359,11 @@ static int swap_staged_impl(const hfk_swap_desc *d, const void *slots_host, void
         if (to_staging) {
           auto kern = kv_swap_bulk_kernel<true, decltype(lag)::value>;
           if ((err = allow_smem(kern, p.smem)) != cudaSuccess) return err;
-          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
+          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, swap_id_tile(n));
         } else {
           auto kern = kv_swap_bulk_kernel<false, decltype(lag)::value>;
           if ((err = allow_smem(kern, p.smem)) != cudaSuccess) return err;
-          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages);
+          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, swap_id_tile(n));
         }
         return cudaGetLastError();
       });

@@ -40,12 +40,24 @@ __device__ __forceinline__ int64_t load_id(const void *ids, int is64, int64_t i)
               : (int64_t) reinterpret_cast<const int32_t *>(ids)[i];
 }
 
-// Shared-memory image common to both movers.
+// Shared-memory image common to both movers: id_tile device offsets, id_tile host offsets, then
+// 2*layers pointers (K then V).  id_tile = min(n_blocks, kSwapIdTile), so a small launch has a
+// small footprint and its CTAs fit next to a compute kernel's on an SM.
 struct SwapTables {
-  int64_t dev_off[kSwapIdTile];
-  int64_t host_off[kSwapIdTile];
-  // followed by 2*layers pointers (K then V)
+  int64_t *dev_off;
+  int64_t *host_off;
+  unsigned char **layer_ptrs;
 };
+__host__ __device__ inline size_t swap_tables_bytes(int id_tile, int layers) {
+  return (size_t)id_tile * 2 * sizeof(int64_t) + (size_t)layers * 2 * sizeof(void *);
+}
+__device__ __forceinline__ SwapTables carve_swap_tables(unsigned char *base, int id_tile) {
+  SwapTables t;
+  t.dev_off = reinterpret_cast<int64_t *>(base);
+  t.host_off = t.dev_off + id_tile;
+  t.layer_ptrs = reinterpret_cast<unsigned char **>(t.host_off + id_tile);
+  return t;
+}
 
 __device__ __forceinline__ void stage_layer_ptrs(const SwapArgs &a, unsigned char **lp) {
   for (int l = threadIdx.x; l < a.layers; l += blockDim.x) {
@@ -54,7 +66,7 @@ __device__ __forceinline__ void stage_layer_ptrs(const SwapArgs &a, unsigned cha
   }
 }
 
-__device__ __forceinline__ void stage_ids(const SwapArgs &a, SwapTables *t, int64_t tile0, int tn) {
+__device__ __forceinline__ void stage_ids(const SwapArgs &a, const SwapTables *t, int64_t tile0, int tn) {
   for (int i = threadIdx.x; i < tn; i += blockDim.x) {
     const int64_t d = load_id(a.device_block_ids, a.ids_are_int64, tile0 + i);
     // a null slot list means "slot = position in the list" (dense staging buffer)
@@ -74,15 +86,16 @@ __device__ __forceinline__ void stage_ids(const SwapArgs &a, SwapTables *t, int6
 // with a block-major host pool the grid as a whole streams the host memory of a
 // slot front to back.
 template <bool kToHost, int kThreads, int kUnroll>
-__global__ void __launch_bounds__(kThreads) kv_swap_vector_kernel(SwapArgs a) {
+__global__ void __launch_bounds__(kThreads) kv_swap_vector_kernel(SwapArgs a, int id_tile) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  SwapTables *t = reinterpret_cast<SwapTables *>(smem_raw);
-  unsigned char **lp = reinterpret_cast<unsigned char **>(smem_raw + sizeof(SwapTables));
+  const SwapTables tables = carve_swap_tables(smem_raw, id_tile);
+  const SwapTables *t = &tables;
+  unsigned char **lp = tables.layer_ptrs;
   stage_layer_ptrs(a, lp);
   const int per_block = 2 * a.layers;
   const int64_t n16 = a.block_bytes >> 4;
-  for (int64_t tile0 = 0; tile0 < a.n_blocks; tile0 += kSwapIdTile) {
-    const int tn = (int)min((int64_t)kSwapIdTile, a.n_blocks - tile0);
+  for (int64_t tile0 = 0; tile0 < a.n_blocks; tile0 += id_tile) {
+    const int tn = (int)min((int64_t)id_tile, a.n_blocks - tile0);
     __syncthreads();  // previous tile fully consumed
     stage_ids(a, t, tile0, tn);
     __syncthreads();
@@ -111,14 +124,13 @@ __global__ void __launch_bounds__(kThreads) kv_swap_vector_kernel(SwapArgs a) {
 // PumpSmem, then SwapTables, then the layer pointers.
 template <bool kToHost, int kLag>
 __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_bytes,
-                                                          int n_stages) {
+                                                          int n_stages, int id_tile) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char *stages = smem_raw;
   PumpSmem *ps = reinterpret_cast<PumpSmem *>(smem_raw + (size_t)stage_bytes * n_stages);
-  SwapTables *t = reinterpret_cast<SwapTables *>(reinterpret_cast<unsigned char *>(ps) +
-                                                 sizeof(PumpSmem));
-  unsigned char **lp =
-      reinterpret_cast<unsigned char **>(reinterpret_cast<unsigned char *>(t) + sizeof(SwapTables));
+  const SwapTables tables = carve_swap_tables(reinterpret_cast<unsigned char *>(ps) + sizeof(PumpSmem), id_tile);
+  const SwapTables *t = &tables;
+  unsigned char **lp = tables.layer_ptrs;
   if (threadIdx.x == 0) {
     for (int s = 0; s < n_stages; ++s) mbar_init(&ps->full[s], 1);
     mbar_fence_init();
@@ -128,8 +140,8 @@ __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_
   const int per_block = 2 * a.layers;
   const int pieces = (int)((a.block_bytes + stage_bytes - 1) / stage_bytes);
   uint32_t seq = 0;
-  for (int64_t tile0 = 0; tile0 < a.n_blocks; tile0 += kSwapIdTile) {
-    const int tn = (int)min((int64_t)kSwapIdTile, a.n_blocks - tile0);
+  for (int64_t tile0 = 0; tile0 < a.n_blocks; tile0 += id_tile) {
+    const int tn = (int)min((int64_t)id_tile, a.n_blocks - tile0);
     __syncwarp();
     stage_ids(a, t, tile0, tn);
     __syncwarp();
