@@ -253,3 +253,35 @@ def test_torch_ops_are_registered_with_reference_schemas():
     # no CPU implementation of any kernel: an all-CPU call is refused by the dispatcher
     with pytest.raises(NotImplementedError):
         torch.ops.pcie_through.gather(torch.zeros(4, 4), torch.zeros(2, 4), torch.zeros(2, dtype=torch.long))
+
+
+def test_registry_is_safe_under_concurrent_registration_and_lookup(registry):
+    """Lookups take the shared lock, mutations the exclusive one (managed_mem.cpp:31,47,143)."""
+    import threading
+
+    lib = registry
+    bufs = [torch.zeros(4096, dtype=torch.uint8) for _ in range(64)]
+    errors = []
+
+    def writer(lo, hi):
+        for _ in range(20):
+            for b in bufs[lo:hi]:
+                if not lib.hfk_register_ptr(b.data_ptr(), b.numel()):
+                    errors.append("register failed")
+            for b in bufs[lo:hi]:
+                lib.hfk_unregister_ptr(b.data_ptr())
+
+    def reader():
+        for _ in range(2000):
+            for b in bufs[::7]:
+                alias = lib.hfk_get_device_ptr(b.data_ptr() + 5)
+                if alias not in (0, b.data_ptr() + 5):
+                    errors.append("wrong alias")
+
+    threads = [threading.Thread(target=writer, args=(i * 16, (i + 1) * 16)) for i in range(4)]
+    threads += [threading.Thread(target=reader) for _ in range(3)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert errors == [] and lib.hfk_registry_count() == 0
