@@ -578,6 +578,7 @@ def main() -> None:
     ap.add_argument("--gather-aiv", type=int, default=0)
     ap.add_argument("--host-slots", type=int, default=0, help="override the host pool size (slots)")
     ap.add_argument("--device-blocks", type=int, default=0, help="override the device cache size (blocks)")
+    ap.add_argument("--no-spread", action="store_true", help="use GPU ordinal = LOCAL_RANK even when more GPUs are visible")
     ap.add_argument("--no-gather", action="store_true")
     ap.add_argument("--gather-only", action="store_true", help="run only the paged-gather leg")
     ap.add_argument("--gather-seqs", type=int, default=64, help="sequences in the gather batch")
@@ -619,8 +620,10 @@ def main() -> None:
     pkg.load_ops()
     if args.gather_hints >= 0:
         pkg.capi.check(pkg.capi.lib().hfk_set_gather_tuning(args.gather_hints, -1), "hfk_set_gather_tuning")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
+    # fewer ranks than visible GPUs: spread them over the PCI bus order (ranks.spread_device_index)
+    dev_index = local_rank if args.no_spread else ranks.spread_device_index(local_rank, world, torch.cuda.device_count())
+    torch.cuda.set_device(dev_index)
+    device = torch.device("cuda", dev_index)
     ctx.init("nccl", device)
     barrier, max_over_ranks = ctx.barrier, ctx.max_over_ranks
 
@@ -659,7 +662,9 @@ def main() -> None:
     fill_random_bytes(cache._v_store, 200 + rank)
     config.update({"host_slots": host_slots, "host_pool_bytes": host_slots * slot_bytes, "pool_note": pool_note,
                    "host_pool_layout": "[slot][layer][K|V][block] (2 MiB-class contiguous per slot)",
-                   "numa_node": pkg.memory.device_numa_node(), "pool_setup_s": round(setup_pool_s, 2)})
+                   "numa_node": pkg.memory.device_numa_node(), "pool_setup_s": round(setup_pool_s, 2),
+                   "gpu_ordinal_of_rank": "spread over the visible GPUs in PCI bus order" if not args.no_spread
+                   else "LOCAL_RANK", "visible_gpus": torch.cuda.device_count()})
 
     n_sets = args.warmup + args.steps
     sets = ranks.rank_id_sets(rank, n_sets, g.n_swap, g.num_blocks, host_slots)
@@ -706,7 +711,7 @@ def main() -> None:
         return evs
 
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sampler = ClockSampler(dev_index) if rank == 0 else None
     evs = run_value()
     clocks = sampler.stop() if sampler else None
     total_ms = max_over_ranks(t_start.elapsed_time(t_end))

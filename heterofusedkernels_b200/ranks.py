@@ -68,6 +68,16 @@ class RankContext:
         self.dist = None
 
 
+def spread_device_index(local_rank: int, world: int, visible: int) -> int:
+    """GPU ordinal for a local rank when fewer ranks than visible GPUs run: ranks are spread evenly
+    over the ordinals (0 and 4 of 8 for two ranks, 0, 2, 4, 6 for four).  CUDA orders devices by PCI
+    bus, so neighbouring ordinals tend to hang off the same host bridge; spreading the ranks gives each
+    its own share of the host's PCIe and memory paths.  With world == visible it is the identity."""
+    if visible <= 0 or world >= visible:
+        return local_rank % max(visible, 1)
+    return (local_rank * visible) // world
+
+
 def rank_id_sets(rank: int, n_sets: int, n_swap: int, num_blocks: int, host_slots: int,
                  seed: int = 1234) -> List[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]:
     """Per-rank seeded id lists for `n_sets` steps: (device ids to swap out, host slots, device ids to

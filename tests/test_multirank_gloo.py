@@ -67,3 +67,11 @@ def test_host_pool_is_shrunk_per_rank_but_never_below_the_transferred_set():
     slots, note = ranks.host_pool_slots(40000, slot, 512, 8, 200 << 30)
     assert slots == int((200 << 30) * 0.6 / 8) // slot and "shrunk" in note
     assert ranks.host_pool_slots(40000, slot, 512, 8, 1 << 30)[0] == 1024
+
+
+def test_ranks_are_spread_over_the_visible_gpus():
+    assert [ranks.spread_device_index(r, 2, 8) for r in range(2)] == [0, 4]
+    assert [ranks.spread_device_index(r, 4, 8) for r in range(4)] == [0, 2, 4, 6]
+    assert [ranks.spread_device_index(r, 8, 8) for r in range(8)] == list(range(8))
+    assert [ranks.spread_device_index(r, 2, 2) for r in range(2)] == [0, 1]
+    assert ranks.spread_device_index(0, 1, 8) == 0 and ranks.spread_device_index(3, 4, 1) == 0
