@@ -579,6 +579,7 @@ def main() -> None:
     ap.add_argument("--host-slots", type=int, default=0, help="override the host pool size (slots)")
     ap.add_argument("--device-blocks", type=int, default=0, help="override the device cache size (blocks)")
     ap.add_argument("--no-spread", action="store_true", help="use GPU ordinal = LOCAL_RANK even when more GPUs are visible")
+    ap.add_argument("--stagger", type=int, default=1, help="N > 1: odd ranks run swap-in before swap-out (1) or not (0)")
     ap.add_argument("--no-gather", action="store_true")
     ap.add_argument("--gather-only", action="store_true", help="run only the paged-gather leg")
     ap.add_argument("--gather-seqs", type=int, default=64, help="sequences in the gather batch")
@@ -664,7 +665,9 @@ def main() -> None:
                    "host_pool_layout": "[slot][layer][K|V][block] (2 MiB-class contiguous per slot)",
                    "numa_node": pkg.memory.device_numa_node(), "pool_setup_s": round(setup_pool_s, 2),
                    "gpu_ordinal_of_rank": "spread over the visible GPUs in PCI bus order" if not args.no_spread
-                   else "LOCAL_RANK", "visible_gpus": torch.cuda.device_count()})
+                   else "LOCAL_RANK", "visible_gpus": torch.cuda.device_count(),
+                   "direction_order": "odd ranks swap-in first, even ranks swap-out first" if (args.stagger and world > 1)
+                   else "swap-out then swap-in on every rank"})
 
     n_sets = args.warmup + args.steps
     sets = ranks.rank_id_sets(rank, n_sets, g.n_swap, g.num_blocks, host_slots)
@@ -691,6 +694,12 @@ def main() -> None:
             cache.swap_in(dev_ids, slots_dev, aiv=aiv, mover=mover)
 
     # ---- value leg: ids resident on the device, kernels only -----------------------------
+    # With several ranks the odd ones run each step's two calls in the other order (swap-in of a slot
+    # set first, then the swap-out), so that at any time about half the links carry host->device and
+    # half device->host traffic: the host's paths are full duplex, and all ranks writing at once or
+    # all reading at once leaves one direction idle.
+    in_first = bool(args.stagger and world > 1 and rank % 2 == 1)
+
     def run_value():
         evs = []
         for s in range(n_sets):
@@ -700,9 +709,15 @@ def main() -> None:
                 t_start.record()
             e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
             e[0].record()
-            do_out(o_ids, slots, sets[s][1])
+            if in_first:
+                do_in(i_ids, slots, sets[s][1])
+            else:
+                do_out(o_ids, slots, sets[s][1])
             e[1].record()
-            do_in(i_ids, slots, sets[s][1])
+            if in_first:
+                do_out(o_ids, slots, sets[s][1])
+            else:
+                do_in(i_ids, slots, sets[s][1])
             e[2].record()
             if s >= args.warmup:
                 evs.append(e)
@@ -716,8 +731,9 @@ def main() -> None:
     clocks = sampler.stop() if sampler else None
     total_ms = max_over_ranks(t_start.elapsed_time(t_end))
     ms_per_step = total_ms / args.steps
-    out_ms = [e[0].elapsed_time(e[1]) for e in evs]
-    in_ms = [e[1].elapsed_time(e[2]) for e in evs]
+    first_ms = [e[0].elapsed_time(e[1]) for e in evs]
+    second_ms = [e[1].elapsed_time(e[2]) for e in evs]
+    out_ms, in_ms = (second_ms, first_ms) if in_first else (first_ms, second_ms)
     status = cache.status()
     value = ranks.aggregate_gbs(2 * g.swap_bytes, world, ms_per_step)
     bus = (C.c_char * 32)()
@@ -734,8 +750,12 @@ def main() -> None:
         if s == args.warmup:
             barrier()
             e2e_start.record()
-        do_out(o_ids, slots, sets[s][1])     # ids: pinned host -> device inside the call
-        do_in(i_ids, slots, sets[s][1])
+        if in_first:
+            do_in(i_ids, slots, sets[s][1])  # ids: pinned host -> device inside the call
+            do_out(o_ids, slots, sets[s][1])
+        else:
+            do_out(o_ids, slots, sets[s][1])
+            do_in(i_ids, slots, sets[s][1])
         status_host[0] = cache.status()                         # device -> host read of the step's result
     e2e_end.record()
     barrier()
