@@ -6,14 +6,18 @@ paged gather in HBM (secondary, single-GPU runs).
     python bench.py --impl reference ...                    # the CPU restatement on the host cores
 
 A *step* is one pass of the hot path over one batch: one swap-out call (HBM -> pinned host pool)
-followed by one swap-in call (host pool -> HBM, other device blocks) of the workload's block
-count, all layers, K and V.  Each rank owns its own cache, pool and PCIe link; there is no
-collective on the data path, so scaling is weak (per-GPU work fixed).  torch.distributed is used
-only for the start barrier and the max-over-ranks reduction of the device-side time.
+and one swap-in call (host pool -> HBM, other device blocks) of the workload's block count, all
+layers, K and V.  Each rank owns its own cache, pool and PCIe link; there is no collective on the
+data path, so scaling is weak (per-GPU work fixed).  torch.distributed is used only for the start
+barrier and the max-over-ranks reduction of the device-side time.
 
-Prints ONE JSON line (rank 0).  `value` is the whole-job GB/s with the id lists resident on the
-device; `e2e` drives the same step through the public API (PagedKVCache.swap_out / swap_in) with
-host-resident id lists and reads the status word back every step.
+Prints ONE JSON line (rank 0).  `value` is the whole-job GB/s of the Llama-3-8B step with the id
+lists resident on the device; `e2e` drives the same step through the public API
+(PagedKVCache.swap_out / swap_in) with host-resident id lists and reads the status word back every
+step.  Every timed leg is followed by a byte-for-byte check of what its last step moved
+(`verified`).  The same line carries short runs of the other configurations as flat objects:
+`config4` (Llama-3-70B TP8 shard, every N), `overlap` (layer-wise prefetch next to a GEMM, N = 1)
+and `gather` (paged gather, N = 1); the scalars a reader needs first are repeated inside `roofline`.
 """
 from __future__ import annotations
 
@@ -32,6 +36,8 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 import torch  # noqa: E402
+
+from heterofusedkernels_b200 import workloads as wl  # noqa: E402
 
 GB = 1e9
 
@@ -83,6 +89,15 @@ def fill_random_bytes(t: torch.Tensor, seed: int) -> None:
         part.copy_(torch.randint(0, 254, part.shape, dtype=torch.uint8, device=t.device, generator=gen))
         if t.element_size() == 1:
             part += (part >= 0x7F).to(torch.uint8)
+
+
+def traffic_ratio(kernel: str, default: float) -> tuple:
+    """DRAM bytes per algorithmic byte of a kernel, from the tracked summary of its ncu capture."""
+    try:
+        entry = json.loads((ROOT / "profiles" / "traffic.json").read_text())[kernel]
+        return float(entry["dram_bytes_per_algorithmic_byte"]), entry["source"]
+    except (OSError, KeyError, ValueError):
+        return default, "profiles/traffic.json missing: ratio assumed"
 
 
 class ClockSampler:
@@ -148,9 +163,9 @@ def cpu_baseline_swap(g, steps: int, warmup: int, budget_s: float = 25.0) -> dic
     times = []
     t_start = time.perf_counter()
     for s in range(warmup + steps):
-        ids = o.distinct_ids(g.n_swap, nb, 10 + s)
-        slots = o.distinct_ids(g.n_swap, nb, 20 + s)
-        back = o.distinct_ids(g.n_swap, nb, 30 + s)
+        ids = wl.distinct_ids(g.n_swap, nb, 10 + s)
+        slots = wl.distinct_ids(g.n_swap, nb, 20 + s)
+        back = wl.distinct_ids(g.n_swap, nb, 30 + s)
         t0 = time.perf_counter()
         o.swap_out(dev_k, dev_v, pool, ids, slots)
         o.swap_in(dev_k, dev_v, pool, back, slots)
@@ -192,12 +207,15 @@ def measure_pcie_peak(pool_u8: torch.Tensor, device) -> dict:
 
 
 def measure_pcie_concurrent(ctx, pool_u8: torch.Tensor, device) -> dict:
-    """cudaMemcpyAsync rate with EVERY rank copying at the same time: 8 back-to-back copies of 1 GiB per
-    direction after a barrier.  This is the denominator for N > 1: what the host (root complexes, memory)
-    gives N links at once, as opposed to one link alone."""
-    n = min(pool_u8.numel(), 1 << 30)
-    host = pool_u8[:n]
+    """cudaMemcpyAsync rates with EVERY rank copying at the same time, after a barrier: 8 back-to-back
+    copies of 1 GiB in one direction (h2d, d2h), and 4 + 4 copies in both directions at once on two
+    streams (bidir: both directions' bytes over the time until both are done).  These are the
+    denominators for N > 1: what the host (root complexes, memory) gives N links at once, as opposed
+    to one link alone."""
+    n = min(pool_u8.numel() // 2, 1 << 30)
+    host, host2 = pool_u8[:n], pool_u8[n:2 * n]
     dev = torch.empty(n, dtype=torch.uint8, device=device)
+    dev2 = torch.empty(n, dtype=torch.uint8, device=device)
     res = {}
     for name, dst, src in (("h2d", dev, host), ("d2h", host, dev)):
         dst.copy_(src, non_blocking=True)
@@ -210,19 +228,227 @@ def measure_pcie_concurrent(ctx, pool_u8: torch.Tensor, device) -> dict:
         b.synchronize()
         res[name] = 8 * n / (a.elapsed_time(b) * 1e-3) / GB
         ctx.barrier()
-    del dev
+    s1, s2 = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    main = torch.cuda.current_stream(device)
+    ctx.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    s1.wait_event(a)
+    s2.wait_event(a)
+    with torch.cuda.stream(s1):
+        for _ in range(4):
+            host.copy_(dev, non_blocking=True)       # d2h
+    with torch.cuda.stream(s2):
+        for _ in range(4):
+            dev2.copy_(host2, non_blocking=True)     # h2d
+    main.wait_stream(s1)
+    main.wait_stream(s2)
+    b.record()
+    b.synchronize()
+    res["bidir_total"] = 8 * n / (a.elapsed_time(b) * 1e-3) / GB
+    ctx.barrier()
+    del dev, dev2
     return res
+
+
+# --------------------------------------------------------------------------- verification
+def _pool_bytes(cache) -> torch.Tensor:
+    """[slots, layers, 2, block_bytes] byte view of the host pool."""
+    return cache.host_pool.view(torch.uint8).view(cache.host_slots, cache.layers, 2, cache.block_bytes)
+
+
+def _cache_bytes(cache, kv: int, layer: int) -> torch.Tensor:
+    t = (cache.v_caches if kv else cache.k_caches)[layer]
+    return t.view(torch.uint8).view(cache.num_blocks, cache.block_bytes)
+
+
+def verify_swap(cache, pairs, layers=None) -> dict:
+    """Byte-for-byte check of swapped data: for every (device ids, host slots) pair list, every layer
+    and K and V, cache[block] must equal pool[slot].  The device blocks are compared with the host
+    slots on the device, 64 MiB at a time; a small sample also goes through the CPU oracle."""
+    from oracle import kv_oracle as o
+
+    pool = _pool_bytes(cache)
+    layers = range(cache.layers) if layers is None else layers
+    bad, checked = [], 0
+    for name, dev_ids, slots in pairs:
+        dev_ids_d = dev_ids.to(cache.device)
+        slots_c = slots.cpu()
+        for l in layers:
+            for kv in (0, 1):
+                want = pool[:, l, kv].index_select(0, slots_c).to(cache.device, non_blocking=True)
+                got = _cache_bytes(cache, kv, l).index_select(0, dev_ids_d)
+                checked += want.numel()
+                if not torch.equal(got, want):
+                    bad.append((name, l, kv))
+        # the oracle on a sample: three blocks, first and last layer
+        n = min(3, dev_ids.numel())
+        ls = sorted({layers[0], layers[-1]}) if len(layers) else []
+        if n and ls:
+            small_k = [_cache_bytes(cache, 0, l).index_select(0, dev_ids_d[:n]).cpu() for l in ls]
+            small_v = [_cache_bytes(cache, 1, l).index_select(0, dev_ids_d[:n]).cpu() for l in ls]
+            ref = torch.zeros((n, len(ls), 2, cache.block_bytes), dtype=torch.uint8)
+            o.swap_out(small_k, small_v, ref, torch.arange(n), torch.arange(n))
+            have = pool.index_select(0, slots_c[:n])[:, ls]
+            if not torch.equal(ref, have):
+                bad.append((name, "oracle sample"))
+    torch.cuda.synchronize(cache.device)
+    return {"verified": not bad, "bytes_checked": checked, "mismatches": bad[:8]}
+
+
+# --------------------------------------------------------------------------- the swap step
+class SwapBench:
+    """One rank's swap workload: the cache, the pool, the per-step id sets and the ways to run a step.
+
+    Set 0 primes the pool (one untimed swap-out); step s >= 1 uses set s: swap-out of o_ids[s] into
+    slots[s] and swap-in into i_ids[s] (other blocks) from slots[s] ("own": the blocks just swapped
+    out come back) or from slots[s-1] ("prev": the blocks swapped out one step earlier come back,
+    which lets the two directions of a step run independently).
+
+    Variants (`--variant`):
+      sequential  swap-out then swap-in of the same slots, one stream (N = 1 default)
+      stagger     even ranks as sequential; odd ranks swap-in (prev) first, then swap-out
+      bidir       swap-out and swap-in (prev) concurrently on two streams
+      interleave:k  the step's lists cut into k parts, out/in parts alternating on one stream
+                    (odd ranks: in (prev) first)
+    """
+
+    def __init__(self, g, cache, ctx, pkg, n_sets: int, mover, aiv, staging_mb: int, slot_runs: bool = False):
+        self.g, self.cache, self.ctx, self.pkg = g, cache, ctx, pkg
+        self.mover, self.aiv, self.staging_bytes = mover, aiv, staging_mb << 20
+        from heterofusedkernels_b200 import ranks
+
+        self.sets = ranks.rank_id_sets(ctx.rank, n_sets + 1, g.n_swap, g.num_blocks, cache.host_slots)
+        if slot_runs:
+            # the slots of a step form one run of consecutive slots, as a fresh free list hands them
+            # out (HostSlotPool); consecutive steps use different runs
+            n_runs = cache.host_slots // g.n_swap
+            self.sets = [(o_ids, torch.arange(g.n_swap) + (s % n_runs) * g.n_swap, i_ids)
+                         for s, (o_ids, _, i_ids) in enumerate(self.sets)]
+        self.dev_sets = [tuple(t.to(cache.device) for t in s) for s in self.sets]
+        self.pin_sets = [tuple(t.pin_memory() for t in s) for s in self.sets]
+        self.side = [torch.cuda.Stream(cache.device), torch.cuda.Stream(cache.device)]
+        self.launches = 0          # swap calls issued so far
+        self.launches_timed = 0    # ... of which inside the last run's timed region
+
+    # one call each way; ids: device tensors (value leg) or pinned host tensors (e2e leg)
+    def _out(self, ids, slots, slots_cpu):
+        self.launches += 1
+        if self.mover == "staged":
+            self.cache.swap_out_staged(ids, slots_cpu, staging_bytes=self.staging_bytes, aiv=self.aiv)
+        else:
+            self.cache.swap_out(ids, slots, aiv=self.aiv, mover=self.mover)
+
+    def _in(self, ids, slots, slots_cpu):
+        self.launches += 1
+        if self.mover == "staged":
+            self.cache.swap_in_staged(ids, slots_cpu, staging_bytes=self.staging_bytes, aiv=self.aiv)
+        else:
+            self.cache.swap_in(ids, slots, aiv=self.aiv, mover=self.mover)
+
+    def prime(self):
+        o_ids, slots, _ = self.dev_sets[0]
+        self._out(o_ids, slots, self.sets[0][1])
+        torch.cuda.synchronize(self.cache.device)
+
+    def plan(self, variant: str):
+        """(in_source, order, parts, two_streams) of this rank for a variant."""
+        odd = self.ctx.world > 1 and self.ctx.rank % 2 == 1
+        if variant == "sequential":
+            return "own", "out_first", 1, False
+        if variant == "stagger":
+            return ("prev", "in_first", 1, False) if odd else ("own", "out_first", 1, False)
+        if variant == "bidir":
+            return "prev", "out_first", 1, True
+        if variant.startswith("interleave:"):
+            k = max(1, int(variant.split(":")[1]))
+            return ("prev", "in_first", k, False) if odd else ("own", "out_first", k, False)
+        raise ValueError(f"unknown variant {variant}")
+
+    def run(self, variant: str, steps: int, warmup: int, e2e: bool) -> dict:
+        """Runs warmup + steps steps (sets 1..warmup+steps); returns this rank's timings and the
+        verification of the last step."""
+        cache, ctx = self.cache, self.ctx
+        src_mode, order, parts, two = self.plan(variant)
+        use = self.pin_sets if e2e else self.dev_sets
+        main = torch.cuda.current_stream(cache.device)
+        t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        out_ev, in_ev = [], []
+        self.prime()
+        status_acc = 0
+        for s in range(1, warmup + steps + 1):
+            o_ids, slots, i_ids = use[s]
+            src_slots = slots if src_mode == "own" else use[s - 1][1]
+            src_slots_cpu = self.sets[s][1] if src_mode == "own" else self.sets[s - 1][1]
+            if s == warmup + 1:
+                ctx.barrier()
+                t_start.record()
+                launches_before = self.launches
+            timed = s > warmup
+            if two:
+                fork = torch.cuda.Event()
+                fork.record()
+                evs = []
+                for stream, fn, args in ((self.side[0], self._out, (o_ids, slots, self.sets[s][1])),
+                                         (self.side[1], self._in, (i_ids, src_slots, src_slots_cpu))):
+                    stream.wait_event(fork)
+                    with torch.cuda.stream(stream):
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record()
+                        fn(*args)
+                        b.record()
+                    evs.append((a, b))
+                main.wait_stream(self.side[0])
+                main.wait_stream(self.side[1])
+                if timed:
+                    out_ev.append([evs[0]])
+                    in_ev.append([evs[1]])
+            else:
+                n = o_ids.numel()
+                cuts = [(n * j) // parts for j in range(parts + 1)]
+                step_out, step_in = [], []
+                for j in range(parts):
+                    lo, hi = cuts[j], cuts[j + 1]
+                    calls = [("out", self._out, (o_ids[lo:hi], slots[lo:hi], self.sets[s][1][lo:hi])),
+                             ("in", self._in, (i_ids[lo:hi], src_slots[lo:hi], src_slots_cpu[lo:hi]))]
+                    if order == "in_first":
+                        calls.reverse()
+                    for kind, fn, args in calls:
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record()
+                        fn(*args)
+                        b.record()
+                        (step_out if kind == "out" else step_in).append((a, b))
+                if timed:
+                    out_ev.append(step_out)
+                    in_ev.append(step_in)
+            if e2e:
+                status_acc |= cache.status()    # device -> host read of the step's result
+        t_end.record()
+        self.launches_timed = self.launches - launches_before
+        ctx.barrier()
+        status = status_acc | cache.status()
+        last = warmup + steps
+        o_ids, slots, i_ids = self.sets[last]
+        src = slots if src_mode == "own" else self.sets[last - 1][1]
+        ver = verify_swap(cache, [("swap_out", o_ids, slots), ("swap_in", i_ids, src)])
+        out_ms = [sum(a.elapsed_time(b) for a, b in st) for st in out_ev]
+        in_ms = [sum(a.elapsed_time(b) for a, b in st) for st in in_ev]
+        return {"local_ms_per_step": t_start.elapsed_time(t_end) / steps, "out_ms": out_ms, "in_ms": in_ms,
+                "status": status, "verified": ver["verified"] and status == 0, "verify": ver,
+                "plan": {"swap_in_source": src_mode, "order": order, "parts": parts, "two_streams": two}}
 
 
 # --------------------------------------------------------------------------- gather leg
 def bench_gather(device, steps: int, warmup: int, mover, aiv, num_seqs: int = 64) -> dict:
     """Paged gather, Llama-3-8B layout: 64 sequences of 512..8192 tokens (seeded), block tables that are
-    disjoint slices of a seeded permutation of a 40000-block cache, all 32 layers, K and V, one launch."""
+    disjoint slices of a seeded permutation of a 40000-block cache, all 32 layers, K and V, one launch.
+    After the timed launches every sequence of every layer, K and V, is compared with a device-side
+    index_select of the same pages."""
     from heterofusedkernels_b200.connector import PagedKVCache
-    from oracle import kv_oracle as o
 
     layers, nblocks, bs, heads, hd = 32, 40000, 16, 8, 128
-    lens = o.gather_seq_lens(seed=0)[:num_seqs]
+    lens = wl.gather_seq_lens(seed=0)[:num_seqs]
     total = sum(lens)
     if num_seqs < 64:  # reduced batch (profiling): a cache just large enough for it
         nblocks = sum((n + bs - 1) // bs for n in lens) + 256
@@ -237,7 +463,8 @@ def bench_gather(device, steps: int, warmup: int, mover, aiv, num_seqs: int = 64
     cache = PagedKVCache(layers, nblocks, bs, heads, hd, torch.bfloat16, device)
     fill_random_bytes(cache._k_store, 1)
     fill_random_bytes(cache._v_store, 2)
-    tables = o.block_tables_for(lens, bs, nblocks, seed=1).to(device)
+    tables_cpu = wl.block_tables_for(lens, bs, nblocks, seed=1)
+    tables = tables_cpu.to(device)
     lens_t = torch.tensor(lens, device=device)
     k_out = torch.empty((layers, total, heads, hd), dtype=torch.bfloat16, device=device)
     v_out = torch.empty_like(k_out)
@@ -252,16 +479,26 @@ def bench_gather(device, steps: int, warmup: int, mover, aiv, num_seqs: int = 64
     torch.cuda.synchronize()
     ms = [a.elapsed_time(b) for a, b in ev]
     status = cache.status()
-    # spot check against torch indexing on the device (layer 3, K, sequence 5)
-    s5 = min(5, len(lens) - 1)
-    nb5 = (lens[s5] + bs - 1) // bs
-    ref = cache.k_caches[3][tables[s5, :nb5]].flatten(0, 1)[:lens[s5]]
-    start = sum(lens[:s5])
-    ok = torch.equal(ref.view(torch.int16), k_out[3, start:start + lens[s5]].view(torch.int16))
+    # full check: token t of the batch lives in cache row block*block_size + offset
+    rows = []
+    for s, n in enumerate(lens):
+        nb = (n + bs - 1) // bs
+        r = (tables_cpu[s, :nb].unsqueeze(1) * bs + torch.arange(bs).unsqueeze(0)).reshape(-1)[:n]
+        rows.append(r)
+    rows = torch.cat(rows).to(device)
+    bad = []
+    for l in range(layers):
+        for name, caches, out in (("K", cache.k_caches, k_out), ("V", cache.v_caches, v_out)):
+            ref = caches[l].view(torch.int16).view(nblocks * bs, heads * hd).index_select(0, rows)
+            if not torch.equal(ref, out[l].view(torch.int16).view(total, heads * hd)):
+                bad.append((l, name))
     mean_ms = sum(ms) / len(ms)
     res = {"workload": "llama3_8b_gather", "total_tokens": total, "num_seqs": len(lens), "layers": layers,
-           "algorithmic_bytes": algo, "ms_per_launch": mean_ms, "best_ms": min(ms),
-           "value": algo / (mean_ms * 1e-3) / GB, "unit": "GB/s", "status_word": status, "spot_check_ok": bool(ok),
+           "cache_blocks": nblocks, "algorithmic_bytes": algo, "ms_per_launch": mean_ms, "best_ms": min(ms),
+           "value": algo / (mean_ms * 1e-3) / GB, "unit": "GB/s", "status_word": status,
+           "verified": not bad and status == 0,
+           "verify": {"what": f"all {len(lens)} sequences x {layers} layers x K,V against a device-side index_select",
+                      "bytes_checked": 2 * layers * total * token_bytes, "mismatches": bad[:8]},
            "note": note}
     del cache, k_out, v_out
     torch.cuda.empty_cache()
@@ -301,16 +538,17 @@ def bench_embedding_gather(device, args, pkg) -> dict:
         # combine: 10x the ids in one call
         big_ids = ids.view(run_count // 10, 10 * bs)
         big_dst = torch.empty((10 * bs, dim), dtype=torch.float16, device=device)
-        for r in range(5):
-            op(table, big_dst, big_ids[r], None)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for r in range(run_count // 10):
-            op(table, big_dst, big_ids[r], None)
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        row["combine_ms_per_call"] = dt / (run_count // 10) * 1e3
-        row["combine_GBps"] = bs * run_count * dim * 2 / dt / GB
+        for label, aiv in (("", None), ("_aiv8", 8), ("_aiv16", 16), ("_aiv64", 64)):
+            for r in range(5):
+                op(table, big_dst, big_ids[r], aiv)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for r in range(run_count // 10):
+                op(table, big_dst, big_ids[r], aiv)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            row["combine_ms_per_call" + label] = dt / (run_count // 10) * 1e3
+            row["combine_GBps" + label] = bs * run_count * dim * 2 / dt / GB
         ok = ok and torch.equal(big_dst.cpu().view(torch.int16),
                                 table[big_ids[run_count // 10 - 1].cpu()].view(torch.int16))
         # CUDA graph of 10 calls (ten different id rows), replayed
@@ -424,144 +662,321 @@ def bench_block_transfer(device, args, pkg) -> dict:
 
 
 # --------------------------------------------------------------------------- overlap leg
-def bench_overlap(g, device, args, pkg) -> dict:
+class OverlapBench:
     """Layer-wise prefetch pipeline (Qwen2-7B-style fp8 cache, 28 layers): while a bf16
-    [8192x3584]x[3584x18944] GEMM runs for layer l on the main stream, 256 blocks of layer l+1 are
-    swapped in on a side stream and 256 other blocks of layer l are swapped out on a second one.
-    Reports swap GB/s per direction under overlap and the GEMM slowdown, per data mover."""
-    from heterofusedkernels_b200.connector import LayerwisePrefetcher, PagedKVCache
+    [8192x3584]x[3584x18944] GEMM runs for layer l on the main stream, 256 blocks of the next layer(s)
+    are swapped in on a side stream and 256 other blocks of layer l are swapped out on a second one,
+    through LayerwisePrefetcher.  `group` layers share one launch per direction (their GEMMs still run
+    one per layer).  Reports swap GB/s per direction under overlap, the GEMM slowdown, and a
+    byte-for-byte check of every block and slot the pipeline touched."""
 
-    cache = PagedKVCache(g.layers, g.num_blocks, g.block_size, g.kv_heads, g.head_dim, g.dtype, device,
-                         host_slots=g.host_slots)
-    fill_random_bytes(cache._k_store, 1)
-    fill_random_bytes(cache._v_store, 2)
-    pf = LayerwisePrefetcher(cache)
-    a = torch.randn(8192, 3584, device=device, dtype=torch.bfloat16)
-    b = torch.randn(3584, 18944, device=device, dtype=torch.bfloat16)
-    c = torch.empty(8192, 18944, device=device, dtype=torch.bfloat16)
-    flops = 2 * 8192 * 3584 * 18944
-    L = g.layers
-    gen = torch.Generator().manual_seed(5)
-    ids = []
-    for l in range(L):
-        perm = torch.randperm(g.num_blocks, generator=gen)
-        sl = torch.randperm(g.host_slots, generator=gen)
-        ids.append((perm[:g.n_swap].to(device), sl[:g.n_swap].to(device),
-                    perm[g.n_swap:2 * g.n_swap].to(device), sl[g.n_swap:2 * g.n_swap].to(device)))
-    cpu_ids = [tuple(t.cpu() for t in x) for x in ids]
-    layer_bytes = g.n_swap * 2 * g.block_bytes
-    main = torch.cuda.current_stream()
+    MAX_GROUP = 8
 
-    def gemm_pass():
+    def __init__(self, g, device, pkg, host_raw=None):
+        from heterofusedkernels_b200.connector import LayerwisePrefetcher, PagedKVCache
+
+        self.g, self.device, self.pkg = g, device, pkg
+        self.cache = PagedKVCache(g.layers, g.num_blocks, g.block_size, g.kv_heads, g.head_dim, g.dtype, device,
+                                  host_slots=g.host_slots if host_raw is None else
+                                  min(g.host_slots, host_raw.numel() // (g.layers * 2 * g.block_bytes)),
+                                  host_raw=host_raw)
+        fill_random_bytes(self.cache._k_store, 1)
+        fill_random_bytes(self.cache._v_store, 2)
+        self.pf = LayerwisePrefetcher(self.cache)
+        self.a = torch.randn(8192, 3584, device=device, dtype=torch.bfloat16)
+        self.b = torch.randn(3584, 18944, device=device, dtype=torch.bfloat16)
+        self.c = torch.empty(8192, 18944, device=device, dtype=torch.bfloat16)
+        self.flops = 2 * 8192 * 3584 * 18944
+        self.L = g.layers
+        gen = torch.Generator().manual_seed(5)
+        # per layer: blocks to bring in / their slots, other blocks to push out / their (other) slots
+        self.ids_cpu = []
+        pool = _pool_bytes(self.cache)
+        for l in range(self.L):
+            perm = torch.randperm(g.num_blocks, generator=gen)
+            sl = torch.randperm(self.cache.host_slots, generator=gen)
+            n = g.n_swap
+            self.ids_cpu.append((perm[:n], sl[:n], perm[n:2 * n], sl[n:2 * n]))
+        self.ids = [tuple(t.to(device) for t in x) for x in self.ids_cpu]
+        # known random bytes wherever a swap-in will read: the in-slots of layer l, for layer l and the
+        # layers a launch that starts at l may cover with it (MAX_GROUP layers per launch at most)
+        rnd = torch.randint(0, 254, (g.n_swap, self.MAX_GROUP) + tuple(pool.shape[2:]), dtype=torch.uint8,
+                            generator=torch.Generator().manual_seed(6))
+        for l in range(self.L):
+            w = min(self.MAX_GROUP, self.L - l)
+            pool[self.ids_cpu[l][1], l:l + w] = rnd[:, :w]
+        self.layer_bytes = g.n_swap * 2 * g.block_bytes
+        self.main = torch.cuda.current_stream(device)
+
+    def warm(self, seconds: float):
+        t = time.perf_counter()
+        while time.perf_counter() - t < seconds:
+            self.gemm_pass()
+
+    def gemm_pass(self) -> float:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(L):
-            torch.matmul(a, b, out=c)
+        for _ in range(self.L):
+            torch.matmul(self.a, self.b, out=self.c)
         e1.record()
         e1.synchronize()
         return e0.elapsed_time(e1)
 
-    def swap_only(kind, ctas):
-        """both directions concurrently, no GEMM: the swap's own rate"""
-        return overlapped(kind, ctas, with_gemm=False)
+    def groups(self, group: int):
+        assert 1 <= group <= self.MAX_GROUP
+        return [range(a, min(a + group, self.L)) for a in range(0, self.L, group)]
 
-    def overlapped(kind, ctas, with_gemm=True):
-        # kind: "vector", "copy_engine", "bulk" (library ring) or "bulk@<stage bytes>x<stages>": smaller
-        # rings let the single-warp CTAs fit next to the GEMM's CTAs on an SM
-        mv = pkg.capi.MOVER_VECTOR if kind == "vector" else (pkg.capi.MOVER_BULK if kind.startswith("bulk") else None)
-        ring = tuple(int(x) for x in kind.split("@")[1].split("x")) if "@" in kind else (0, 0)
-        pkg.capi.lib().hfk_set_bulk_geometry(*ring)
-        ev_in = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L)]
-        ev_out = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L)]
+    def run(self, kind, ctas, group: int = 1, with_gemm: bool = True, directions=("in", "out"), markers=False) -> dict:
+        """One pass over all layers.  kind: None (the prefetcher's shipped defaults), "vector", "bulk",
+        "bulk@<stage bytes>x<stages>" or "copy_engine"."""
+        pkg, pf, cache, L = self.pkg, self.pf, self.cache, self.L
+        lib = pkg.capi.lib()
+        mv = None if kind is None else (pkg.capi.MOVER_VECTOR if kind == "vector" else
+                                        (pkg.capi.MOVER_BULK if kind.startswith("bulk") else None))
+        ring = tuple(int(x) for x in kind.split("@")[1].split("x")) if kind and "@" in kind else (0, 0)
+        lib.hfk_set_bulk_geometry(*ring)
+        groups = self.groups(group)
+        ev_in, ev_out = [], []
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        pf.in_stream.wait_event(e0)
-        pf.out_stream.wait_event(e0)
-        for l in range(L):
-            nxt = (l + 1) % L
-            in_ids, in_slots, out_ids, out_slots = ids[l]
+        for gi, layers in enumerate(groups):
+            nxt = groups[(gi + 1) % len(groups)]
+            in_ids, in_slots, _, _ = self.ids[nxt.start]
+            _, _, out_ids, out_slots = self.ids[layers.start]
             if kind == "copy_engine":
-                ci = cpu_ids[l]
+                ci_n, ci_l = self.ids_cpu[nxt.start], self.ids_cpu[layers.start]
                 with torch.cuda.stream(pf.in_stream):
-                    ev_in[l][0].record()
-                    torch.ops.pcie_through.swap_in_copy_engine(cache.k_ptrs_cpu[nxt:nxt + 1], cache.v_ptrs_cpu[nxt:nxt + 1],
-                                                               pf.pools[nxt], ci[0], ci[1], cache.num_blocks)
-                    ev_in[l][1].record()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    torch.ops.pcie_through.swap_in_copy_engine(cache.k_ptrs_cpu[nxt.start:nxt.stop], cache.v_ptrs_cpu[nxt.start:nxt.stop],
+                                                               cache.host_pool[:, nxt.start:nxt.stop], ci_n[0], ci_n[1], cache.num_blocks)
+                    b.record()
+                ev_in.append((a, b, len(nxt)))
                 with torch.cuda.stream(pf.out_stream):
-                    ev_out[l][0].record()
-                    torch.ops.pcie_through.swap_out_copy_engine(cache.k_ptrs_cpu[l:l + 1], cache.v_ptrs_cpu[l:l + 1],
-                                                                pf.pools[l], ci[2], ci[3], cache.num_blocks)
-                    ev_out[l][1].record()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    torch.ops.pcie_through.swap_out_copy_engine(cache.k_ptrs_cpu[layers.start:layers.stop], cache.v_ptrs_cpu[layers.start:layers.stop],
+                                                                cache.host_pool[:, layers.start:layers.stop], ci_l[2], ci_l[3], cache.num_blocks)
+                    b.record()
+                ev_out.append((a, b, len(layers)))
             else:
-                with torch.cuda.stream(pf.in_stream):
-                    ev_in[l][0].record()
-                pf.prefetch(nxt, in_ids, in_slots, aiv=ctas, mover=mv)
-                with torch.cuda.stream(pf.in_stream):
-                    ev_in[l][1].record()
-                with torch.cuda.stream(pf.out_stream):
-                    ev_out[l][0].record()
-                pf.evict(l, out_ids, out_slots, aiv=ctas, mover=mv)
-                with torch.cuda.stream(pf.out_stream):
-                    ev_out[l][1].record()
+                if "in" in directions:
+                    pf.in_stream.wait_stream(self.main)
+                    with torch.cuda.stream(pf.in_stream):
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        if markers:
+                            lib.hfk_debug_stamp_marker(pf.in_stream.cuda_stream)
+                        a.record()
+                    pf.prefetch(nxt, in_ids, in_slots, aiv=ctas, mover=mv, after=False)
+                    with torch.cuda.stream(pf.in_stream):
+                        b.record()
+                    ev_in.append((a, b, len(nxt)))
+                if "out" in directions:
+                    pf.out_stream.wait_stream(self.main)
+                    with torch.cuda.stream(pf.out_stream):
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        if markers:
+                            lib.hfk_debug_stamp_marker(pf.out_stream.cuda_stream)
+                        a.record()
+                    pf.evict(layers, out_ids, out_slots, aiv=ctas, mover=mv, after=False)
+                    with torch.cuda.stream(pf.out_stream):
+                        b.record()
+                    ev_out.append((a, b, len(layers)))
             if with_gemm:
-                torch.matmul(a, b, out=c)
+                for _ in layers:
+                    torch.matmul(self.a, self.b, out=self.c)
         e1.record()
-        main.wait_stream(pf.in_stream)
-        main.wait_stream(pf.out_stream)
+        pf.quiesce()
         torch.cuda.synchronize()
-        t_in = [x.elapsed_time(y) for x, y in ev_in]
-        t_out = [x.elapsed_time(y) for x, y in ev_out]
-        return {"main_ms": e0.elapsed_time(e1), "in_gbs": layer_bytes / (statistics.median(t_in) * 1e-3) / GB,
-                "out_gbs": layer_bytes / (statistics.median(t_out) * 1e-3) / GB,
-                "in_ms_median": statistics.median(t_in), "out_ms_median": statistics.median(t_out)}
+        lib.hfk_set_bulk_geometry(0, 0)
 
-    # The GEMM runs under the 1 kW power cap, so its time drifts by several percent as the part
-    # warms up.  Warm up for about two seconds, then alternate alone / overlapped passes and compare
-    # medians taken over the same stretch of time.
-    t_warm = time.perf_counter()
-    while time.perf_counter() - t_warm < 2.0:
-        gemm_pass()
-    sampler = ClockSampler(device.index or 0)
-    variants = []
-    alone_all = []
-    reps = 7
-    for kind, ctas in (("bulk", 2), ("bulk", 4), ("bulk", 8), ("bulk", 16), ("bulk@4096x8", 8), ("bulk@4096x8", 16),
-                       ("bulk@2048x4", 32), ("bulk@2048x8", 16), ("bulk@2048x8", 32), ("bulk@2048x8", 64),
-                       ("bulk@4096x4", 16), ("bulk@4096x4", 32), ("vector", 4), ("vector", 8), ("vector", 16),
-                       ("vector", 32), ("copy_engine", 0)):
-        overlapped(kind, ctas)  # warm-up
+        def rate(evs):
+            if not evs:
+                return None, None
+            per = [n * self.layer_bytes / (x.elapsed_time(y) * 1e-3) / GB for x, y, n in evs]
+            return statistics.median(per), statistics.median(x.elapsed_time(y) for x, y, _ in evs)
+
+        in_gbs, in_ms = rate(ev_in)
+        out_gbs, out_ms = rate(ev_out)
+        return {"main_ms": e0.elapsed_time(e1), "in_gbs": in_gbs, "out_gbs": out_gbs, "in_ms_median": in_ms,
+                "out_ms_median": out_ms, "launches": len(ev_in) + len(ev_out)}
+
+    def verify(self, group: int) -> dict:
+        """Every block a swap-in wrote equals its slot and every slot a swap-out wrote equals its block,
+        for the id lists a pass with `group` layers per launch uses."""
+        bad, checked = [], 0
+        groups = self.groups(group)
+        for layers in groups:
+            # both launches that touch this group of layers take their lists from its first layer
+            in_ids, in_slots, out_ids, out_slots = self.ids_cpu[layers.start]
+            r = verify_swap(self.cache, [("swap_in", in_ids, in_slots), ("swap_out", out_ids, out_slots)], layers=layers)
+            checked += r["bytes_checked"]
+            bad += r["mismatches"]
+        return {"verified": not bad, "bytes_checked": checked, "mismatches": bad[:8]}
+
+    def measure(self, kind, ctas, group: int, reps: int) -> dict:
+        self.run(kind, ctas, group)  # warm-up
         alone, runs = [], []
-        for _ in range(reps if kind != "copy_engine" else 3):
-            alone.append(gemm_pass())
-            runs.append(overlapped(kind, ctas))
-        alone_all += alone
+        for _ in range(reps):
+            alone.append(self.gemm_pass())
+            runs.append(self.run(kind, ctas, group))
+        solo = self.run(kind, ctas, group, with_gemm=False)
         t_a = statistics.median(alone)
         med_main = statistics.median(r["main_ms"] for r in runs)
-        solo = swap_only(kind, ctas)
-        variants.append({"mover": kind, "ctas_per_direction": ctas, "gemm_ms_alone": t_a,
-                         "gemm_ms_overlapped": med_main, "gemm_slowdown_pct": 100.0 * (med_main / t_a - 1.0),
-                         "swap_in_gbs": statistics.median(r["in_gbs"] for r in runs),
-                         "swap_out_gbs": statistics.median(r["out_gbs"] for r in runs),
-                         "swap_in_gbs_no_gemm": solo["in_gbs"], "swap_out_gbs_no_gemm": solo["out_gbs"]})
-    pkg.capi.lib().hfk_set_bulk_geometry(0, 0)
-    t_alone = statistics.median(alone_all)
-    t_alone2 = statistics.median([gemm_pass() for _ in range(3)])
+        ver = self.verify(group)
+        return {"mover": kind or "default", "ctas_per_direction": ctas or "default", "layers_per_launch": group,
+                "gemm_ms_alone": t_a, "gemm_ms_overlapped": med_main,
+                "gemm_slowdown_pct": 100.0 * (med_main / t_a - 1.0),
+                "gemm_tflops_alone": self.L * self.flops / (t_a * 1e-3) / 1e12,
+                "swap_in_gbs": statistics.median(r["in_gbs"] for r in runs),
+                "swap_out_gbs": statistics.median(r["out_gbs"] for r in runs),
+                "swap_in_gbs_no_gemm": solo["in_gbs"], "swap_out_gbs_no_gemm": solo["out_gbs"],
+                "launches_per_pass": runs[0]["launches"], "verified": ver["verified"],
+                "bytes_checked": ver["bytes_checked"]}
+
+    def stamps(self, kind, ctas, group: int, direction: str) -> dict:
+        """Scheduling delay of the swap launches of one direction next to the GEMM: a one-thread marker
+        kernel is enqueued in front of every swap launch and every CTA stamps its SM id and its start /
+        end times (the same %globaltimer)."""
+        lib = self.pkg.capi.lib()
+        cap = 8192
+        buf = torch.zeros(1 + 4 * cap, dtype=torch.int64, device=self.device)
+        self.run(kind, ctas, group, directions=(direction,))
+        self.pkg.capi.check(lib.hfk_debug_set_stamps(buf.data_ptr(), buf.numel() * 8), "hfk_debug_set_stamps")
+        self.run(kind, ctas, group, directions=(direction,), markers=True)
+        self.pkg.capi.check(lib.hfk_debug_set_stamps(None, 0), "hfk_debug_set_stamps")
+        w = buf.cpu()
+        n = min(int(w[0]), cap)
+        rec = w[1:1 + 4 * n].view(n, 4)
+        marks = sorted(int(r[2]) for r in rec if (int(r[0]) >> 32) == 0)
+        ctas_rec = [(int(r[0]) & 0xffffffff, int(r[2]), int(r[3])) for r in rec if (int(r[0]) >> 32) != 0]
+        delays, spans, sms, spreads = [], [], set(), []
+        for i, m in enumerate(marks):
+            nxt = marks[i + 1] if i + 1 < len(marks) else 1 << 62
+            mine = [c for c in ctas_rec if m <= c[1] < nxt]
+            if not mine:
+                continue
+            first, last_start, end = min(c[1] for c in mine), max(c[1] for c in mine), max(c[2] for c in mine)
+            delays.append((first - m) * 1e-3)
+            spreads.append((last_start - first) * 1e-3)
+            spans.append((end - first) * 1e-3)
+            sms |= {c[0] for c in mine}
+        med = lambda x: statistics.median(x) if x else None  # noqa: E731
+        return {"mover": kind or "default", "ctas": ctas, "direction": direction, "launches": len(delays),
+                "first_cta_start_after_marker_us_median": med(delays),
+                "first_cta_start_after_marker_us_max": max(delays) if delays else None,
+                "last_cta_start_after_first_us_median": med(spreads),
+                "kernel_span_us_median": med(spans), "distinct_sms": len(sms), "records": n}
+
+
+def overlap_summary(ob: OverlapBench, reps: int, group: int) -> dict:
+    """The `overlap` object of the default line: the prefetcher's shipped defaults."""
+    sampler = ClockSampler(ob.device.index or 0)
+    ob.warm(1.5)
+    m = ob.measure(None, None, group, reps)
     clocks = sampler.stop()
-    status = cache.status()
-    ok = [v for v in variants if v["mover"] in ("bulk", "vector") and v["gemm_slowdown_pct"] < 10.0]
+    status = ob.cache.status()
+    return {"workload": "qwen2_7b_fp8_prefetch", "mover": "LayerwisePrefetcher defaults (vector mover, 16 CTAs per direction)",
+            "layers_per_launch": group, "gemm_slowdown_pct": m["gemm_slowdown_pct"], "swap_in_gbs": m["swap_in_gbs"],
+            "swap_out_gbs": m["swap_out_gbs"], "swap_in_gbs_no_gemm": m["swap_in_gbs_no_gemm"],
+            "swap_out_gbs_no_gemm": m["swap_out_gbs_no_gemm"], "gemm_tflops": m["gemm_tflops_alone"],
+            "gemm_ms_alone": m["gemm_ms_alone"], "gemm_ms_overlapped": m["gemm_ms_overlapped"],
+            "bytes_per_layer_per_direction": ob.layer_bytes, "verified": bool(m["verified"] and status == 0),
+            "bytes_checked": m["bytes_checked"], "status_word": status, "sm_mhz": clocks.get("sm_mhz"),
+            "clock_reasons": ",".join(clocks.get("reasons", [])), "reps": reps}
+
+
+def bench_overlap(g, device, args, pkg) -> dict:
+    """The full overlap study: movers x CTA counts x layers per launch, the large (Llama-3-8B-size)
+    swap next to the GEMM loop, and the scheduling-delay stamps."""
+    ob = OverlapBench(g, device, pkg)
+    ob.warm(2.0)
+    sampler = ClockSampler(device.index or 0)
+    reps = args.overlap_reps
+    variants = []
+    table = [(None, None, 1), (None, None, 2), (None, None, 4), (None, None, 7),
+             ("vector", 8, 1), ("vector", 16, 1), ("vector", 16, 4), ("vector", 32, 4), ("vector", 8, 4),
+             ("bulk", 4, 1), ("bulk", 8, 1), ("bulk", 4, 4), ("bulk@2048x4", 32, 1), ("bulk@2048x4", 32, 4),
+             ("bulk@4096x4", 32, 4), ("copy_engine", 0, 1)]
+    for kind, ctas, group in table:
+        variants.append(ob.measure(kind, ctas, group, reps if kind != "copy_engine" else 2))
+    stamps = []
+    for kind, ctas in (("bulk", 4), ("bulk", 8), ("bulk@2048x4", 32), ("vector", 16)):
+        for direction in ("in", "out"):
+            stamps.append(ob.stamps(kind, ctas, 1, direction))
+    clocks = sampler.stop()
+    status = ob.cache.status()
+    ok = [v for v in variants if v["mover"] != "copy_engine" and v["gemm_slowdown_pct"] < 10.0]
     pick = max(ok or variants, key=lambda v: v["swap_in_gbs"] + v["swap_out_gbs"])
+    L = g.layers
     return {"metric": "kv_swap_GBps_under_gemm_overlap", "value": (pick["swap_in_gbs"] + pick["swap_out_gbs"]) / 2,
             "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": 1, "ms_per_step": pick["gemm_ms_overlapped"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": {"workload": g.name, "layers": L, "blocks_per_layer_per_direction": g.n_swap,
-                       "bytes_per_layer_per_direction": layer_bytes, "kv_dtype": "float8_e4m3fn",
-                       "device_blocks": g.num_blocks, "host_slots": g.host_slots,
+                       "bytes_per_layer_per_direction": ob.layer_bytes, "kv_dtype": "float8_e4m3fn",
+                       "device_blocks": g.num_blocks, "host_slots": ob.cache.host_slots,
                        "gemm": "bf16 [8192x3584]x[3584x18944] per layer (torch.matmul)",
                        "pool sizes": "8192 device / 16384 host blocks (not fixed by the configuration; chosen here)"},
-            "gemm_alone_ms": t_alone, "gemm_alone_ms_after": t_alone2, "gemm_alone_tflops": L * flops / (t_alone * 1e-3) / 1e12,
-            "picked": pick, "variants": variants, "clocks": clocks, "status_word": status,
-            "gpu_launches": 2 * L * reps}
+            "picked": pick, "variants": variants, "stamps": stamps, "clocks": clocks, "status_word": status,
+            "verified": all(v["verified"] for v in variants),
+            "gpu_launches": sum(v["launches_per_pass"] for v in variants) * reps}
+
+
+def bench_large_swap_beside_gemm(sb: SwapBench, device, steps: int) -> dict:
+    """One Llama-3-8B-size swap step (1.07 GB each way) while a GEMM loop occupies the main stream."""
+    a = torch.randn(8192, 3584, device=device, dtype=torch.bfloat16)
+    b = torch.randn(3584, 18944, device=device, dtype=torch.bfloat16)
+    c = torch.empty(8192, 18944, device=device, dtype=torch.bfloat16)
+    side = torch.cuda.Stream(device, priority=-1)
+    main = torch.cuda.current_stream(device)
+
+    def gemms(n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            torch.matmul(a, b, out=c)
+        e1.record()
+        return e0, e1
+
+    t = time.perf_counter()
+    while time.perf_counter() - t < 1.5:
+        e0, e1 = gemms(28)
+        e1.synchronize()
+    n_gemm = 60   # about 50 ms of GEMMs, longer than one swap step
+    alone = []
+    for _ in range(3):
+        e0, e1 = gemms(n_gemm)
+        e1.synchronize()
+        alone.append(e0.elapsed_time(e1))
+    res = []
+    sb.prime()
+    for s in range(1, steps + 1):
+        o_ids, slots, i_ids = sb.dev_sets[s]
+        torch.cuda.synchronize()
+        g0 = torch.cuda.Event()
+        g0.record()
+        side.wait_event(g0)
+        with torch.cuda.stream(side):
+            x0, x1, x2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            x0.record()
+            sb._out(o_ids, slots, sb.sets[s][1])
+            x1.record()
+            sb._in(i_ids, slots, sb.sets[s][1])
+            x2.record()
+        e0, e1 = gemms(n_gemm)
+        main.wait_stream(side)
+        torch.cuda.synchronize()
+        res.append((e0.elapsed_time(e1), x0.elapsed_time(x1), x1.elapsed_time(x2)))
+    ver = verify_swap(sb.cache, [("swap_out", sb.sets[steps][0], sb.sets[steps][1]),
+                                 ("swap_in", sb.sets[steps][2], sb.sets[steps][1])])
+    t_a = statistics.median(alone)
+    return {"gemm_ms_alone": t_a, "gemm_ms_with_swap": statistics.median(r[0] for r in res),
+            "gemm_slowdown_pct": 100.0 * (statistics.median(r[0] for r in res) / t_a - 1.0),
+            "swap_out_gbs": sb.g.swap_bytes / (statistics.median(r[1] for r in res) * 1e-3) / GB,
+            "swap_in_gbs": sb.g.swap_bytes / (statistics.median(r[2] for r in res) * 1e-3) / GB,
+            "note": "the swap step covers about 80 % of the GEMM loop, so the slowdown is diluted by that factor",
+            "verified": ver["verified"]}
 
 
 # --------------------------------------------------------------------------- main
@@ -573,20 +988,32 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="llama3_8b_swap")
     ap.add_argument("--mover", default="auto", choices=["auto", "vector", "bulk", "staged"])
+    ap.add_argument("--variant", default="default",
+                    help="how a step is issued: sequential | stagger | bidir | interleave:<k>; "
+                         "default = sequential on one GPU, the multi-GPU default otherwise")
+    ap.add_argument("--variants", default="", help="comma-separated extra variants to time after the main one")
     ap.add_argument("--staging-mb", type=int, default=1024, help="staging buffer of the staged mover (MiB)")
+    ap.add_argument("--staged-lanes", type=int, default=0, help="copy streams of the staged mover (0 = library default)")
+    ap.add_argument("--slot-runs", action="store_true",
+                    help="each step's host slots form one run of consecutive slots instead of random slots")
     ap.add_argument("--aiv", type=int, default=0, help="CTAs per swap kernel (0 = library default)")
     ap.add_argument("--gather-aiv", type=int, default=0)
     ap.add_argument("--host-slots", type=int, default=0, help="override the host pool size (slots)")
     ap.add_argument("--device-blocks", type=int, default=0, help="override the device cache size (blocks)")
     ap.add_argument("--no-spread", action="store_true", help="use GPU ordinal = LOCAL_RANK even when more GPUs are visible")
-    ap.add_argument("--stagger", type=int, default=1, help="N > 1: odd ranks run swap-in before swap-out (1) or not (0)")
     ap.add_argument("--no-gather", action="store_true")
+    ap.add_argument("--no-config4", action="store_true", help="skip the short Llama-3-70B TP8 run")
+    ap.add_argument("--no-overlap", action="store_true", help="skip the short prefetch-next-to-a-GEMM run")
+    ap.add_argument("--overlap-group", type=int, default=0, help="layers per prefetch launch (0 = shipped default)")
+    ap.add_argument("--overlap-reps", type=int, default=5)
+    ap.add_argument("--beside-gemm", action="store_true", help="also time the full swap step next to a GEMM loop")
     ap.add_argument("--gather-only", action="store_true", help="run only the paged-gather leg")
     ap.add_argument("--gather-seqs", type=int, default=64, help="sequences in the gather batch")
     ap.add_argument("--gather-hints", type=int, default=-1, help="L2 hints of the bulk gather (-1 = library default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "b200":
+        args.warmup = max(args.warmup, 3)
 
     from heterofusedkernels_b200 import ranks
 
@@ -605,9 +1032,9 @@ def main() -> None:
         # the reference semantics (torch CPU index_select / index_copy_ per layer) on the host cores
         if rank != 0:
             return
-        cb = cpu_baseline_swap(g, args.steps, min(args.warmup, 1), budget_s=120.0)
+        cb = cpu_baseline_swap(g, args.steps, args.warmup, budget_s=150.0)
         line = {"impl": "reference", "metric": "kv_swap_GBps", "value": cb["value"], "unit": "GB/s",
-                "n_gpus": args.gpus, "steps": cb["steps"], "warmup": min(args.warmup, 1),
+                "n_gpus": args.gpus, "steps": cb["steps"], "warmup": args.warmup,
                 "ms_per_step": cb["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "u8", "data": "synthetic", "config": config, "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -619,8 +1046,11 @@ def main() -> None:
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     pkg.load_ops()
+    lib = pkg.capi.lib()
     if args.gather_hints >= 0:
-        pkg.capi.check(pkg.capi.lib().hfk_set_gather_tuning(args.gather_hints, -1), "hfk_set_gather_tuning")
+        pkg.capi.check(lib.hfk_set_gather_tuning(args.gather_hints, -1), "hfk_set_gather_tuning")
+    if args.staged_lanes:
+        pkg.capi.check(lib.hfk_set_staged_copy_lanes(args.staged_lanes), "hfk_set_staged_copy_lanes")
     # fewer ranks than visible GPUs: spread them over the PCI bus order (ranks.spread_device_index)
     dev_index = local_rank if args.no_spread else ranks.spread_device_index(local_rank, world, torch.cuda.device_count())
     torch.cuda.set_device(dev_index)
@@ -628,13 +1058,12 @@ def main() -> None:
     ctx.init("nccl", device)
     barrier, max_over_ranks = ctx.barrier, ctx.max_over_ranks
 
-    mover = {"auto": None, "vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK, "staged": None}[args.mover]
-    staged = args.mover == "staged"
+    mover = {"auto": None, "vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK, "staged": "staged"}[args.mover]
     aiv = args.aiv if args.aiv > 0 else None
 
     if args.gather_only:
-        res = bench_gather(device, args.steps, args.warmup, mover, args.gather_aiv if args.gather_aiv > 0 else None,
-                           args.gather_seqs)
+        res = bench_gather(device, args.steps, args.warmup, mover if mover != "staged" else None,
+                           args.gather_aiv if args.gather_aiv > 0 else None, args.gather_seqs)
         print(json.dumps({"metric": "paged_gather_GBps", "value": res["value"], "unit": "GB/s", "n_gpus": 1,
                           "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_launch"],
                           "higher_is_better": True, "dtype": "u8", "data": "synthetic", "gpu_launches": args.steps,
@@ -659,120 +1088,126 @@ def main() -> None:
     cache = PagedKVCache(g.layers, g.num_blocks, g.block_size, g.kv_heads, g.head_dim, g.dtype, device,
                          host_slots=host_slots)
     setup_pool_s = time.perf_counter() - t0
+    host_raw = cache._host_raw
     fill_random_bytes(cache._k_store, 100 + rank)
     fill_random_bytes(cache._v_store, 200 + rank)
+    variant = args.variant
+    if variant == "default":
+        variant = "sequential" if world == 1 else MULTI_GPU_VARIANT
     config.update({"host_slots": host_slots, "host_pool_bytes": host_slots * slot_bytes, "pool_note": pool_note,
                    "host_pool_layout": "[slot][layer][K|V][block] (2 MiB-class contiguous per slot)",
                    "numa_node": pkg.memory.device_numa_node(), "pool_setup_s": round(setup_pool_s, 2),
                    "gpu_ordinal_of_rank": "spread over the visible GPUs in PCI bus order" if not args.no_spread
-                   else "LOCAL_RANK", "visible_gpus": torch.cuda.device_count(),
-                   "direction_order": "odd ranks swap-in first, even ranks swap-out first" if (args.stagger and world > 1)
-                   else "swap-out then swap-in on every rank"})
+                   else "LOCAL_RANK", "visible_gpus": torch.cuda.device_count(), "variant": variant,
+                   "variant_meaning": VARIANT_TEXT.get(variant.split(":")[0], "")})
 
     n_sets = args.warmup + args.steps
-    sets = ranks.rank_id_sets(rank, n_sets, g.n_swap, g.num_blocks, host_slots)
-    dev_sets = [tuple(t.to(device) for t in s) for s in sets]
-    pin_sets = [tuple(t.pin_memory() for t in s) for s in sets]
+    sb = SwapBench(g, cache, ctx, pkg, n_sets, mover, aiv, args.staging_mb, slot_runs=args.slot_runs)
+    config["host_slots_per_step"] = "one run of consecutive slots" if args.slot_runs else "random distinct slots"
 
-    pcie = measure_pcie_peak(cache._host_raw.view(torch.uint8), device) if rank == 0 else None
+    pcie = measure_pcie_peak(host_raw.view(torch.uint8), device) if rank == 0 else None
     barrier()
     pcie_conc = None
     if world > 1:
-        mine = measure_pcie_concurrent(ctx, cache._host_raw.view(torch.uint8), device)
-        pcie_conc = ctx.gather_floats([mine["h2d"], mine["d2h"]])
+        mine = measure_pcie_concurrent(ctx, host_raw.view(torch.uint8), device)
+        pcie_conc = ctx.gather_floats([mine["h2d"], mine["d2h"], mine["bidir_total"]])
 
-    def do_out(dev_ids, slots_dev, slots_cpu):
-        if staged:
-            cache.swap_out_staged(dev_ids, slots_cpu, staging_bytes=args.staging_mb << 20)
-        else:
-            cache.swap_out(dev_ids, slots_dev, aiv=aiv, mover=mover)
-
-    def do_in(dev_ids, slots_dev, slots_cpu):
-        if staged:
-            cache.swap_in_staged(dev_ids, slots_cpu, staging_bytes=args.staging_mb << 20)
-        else:
-            cache.swap_in(dev_ids, slots_dev, aiv=aiv, mover=mover)
+    def timed_leg(bench: SwapBench, var: str, steps: int, warmup: int, e2e: bool) -> dict:
+        r = bench.run(var, steps, warmup, e2e)
+        r["ms_per_step"] = max_over_ranks(r["local_ms_per_step"])
+        r["all_verified"] = max_over_ranks(0.0 if r["verified"] else 1.0) == 0.0
+        r["value"] = ranks.aggregate_gbs(2 * bench.g.swap_bytes, world, r["ms_per_step"])
+        r["out_gbs"] = bench.g.swap_bytes / (statistics.mean(r["out_ms"]) * 1e-3) / GB
+        r["in_gbs"] = bench.g.swap_bytes / (statistics.mean(r["in_ms"]) * 1e-3) / GB
+        return r
 
     # ---- value leg: ids resident on the device, kernels only -----------------------------
-    # With several ranks the odd ones run each step's two calls in the other order (swap-in of a slot
-    # set first, then the swap-out), so that at any time about half the links carry host->device and
-    # half device->host traffic: the host's paths are full duplex, and all ranks writing at once or
-    # all reading at once leaves one direction idle.
-    in_first = bool(args.stagger and world > 1 and rank % 2 == 1)
-
-    def run_value():
-        evs = []
-        for s in range(n_sets):
-            o_ids, slots, i_ids = dev_sets[s]
-            if s == args.warmup:
-                barrier()
-                t_start.record()
-            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-            e[0].record()
-            if in_first:
-                do_in(i_ids, slots, sets[s][1])
-            else:
-                do_out(o_ids, slots, sets[s][1])
-            e[1].record()
-            if in_first:
-                do_out(o_ids, slots, sets[s][1])
-            else:
-                do_in(i_ids, slots, sets[s][1])
-            e[2].record()
-            if s >= args.warmup:
-                evs.append(e)
-        t_end.record()
-        barrier()
-        return evs
-
-    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(dev_index) if rank == 0 else None
-    evs = run_value()
+    val = timed_leg(sb, variant, args.steps, args.warmup, e2e=False)
+    launches_value = sb.launches_timed
     clocks = sampler.stop() if sampler else None
-    total_ms = max_over_ranks(t_start.elapsed_time(t_end))
-    ms_per_step = total_ms / args.steps
-    first_ms = [e[0].elapsed_time(e[1]) for e in evs]
-    second_ms = [e[1].elapsed_time(e[2]) for e in evs]
-    out_ms, in_ms = (second_ms, first_ms) if in_first else (first_ms, second_ms)
-    status = cache.status()
-    value = ranks.aggregate_gbs(2 * g.swap_bytes, world, ms_per_step)
     bus = (C.c_char * 32)()
-    pkg.capi.lib().hfk_device_pci_bus_id(-1, bus, 32)
-    per_rank = ctx.gather_floats([pkg.memory.device_numa_node(), g.swap_bytes / (statistics.mean(out_ms) * 1e-3) / GB,
-                                  g.swap_bytes / (statistics.mean(in_ms) * 1e-3) / GB,
-                                  t_start.elapsed_time(t_end) / args.steps, int(bus.value.decode().split(":")[1], 16)])
+    lib.hfk_device_pci_bus_id(-1, bus, 32)
+    per_rank = ctx.gather_floats([pkg.memory.device_numa_node(), val["out_gbs"], val["in_gbs"],
+                                  val["local_ms_per_step"], int(bus.value.decode().split(":")[1], 16),
+                                  1.0 if val["verified"] else 0.0])
 
     # ---- e2e leg: public API, host-resident id lists, status read back every step ------------
-    e2e_start, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    status_host = torch.zeros(1, dtype=torch.int64)
-    for s in range(n_sets):
-        o_ids, slots, i_ids = pin_sets[s]
-        if s == args.warmup:
-            barrier()
-            e2e_start.record()
-        if in_first:
-            do_in(i_ids, slots, sets[s][1])  # ids: pinned host -> device inside the call
-            do_out(o_ids, slots, sets[s][1])
-        else:
-            do_out(o_ids, slots, sets[s][1])
-            do_in(i_ids, slots, sets[s][1])
-        status_host[0] = cache.status()                         # device -> host read of the step's result
-    e2e_end.record()
-    barrier()
-    e2e_ms = max_over_ranks(e2e_start.elapsed_time(e2e_end)) / args.steps
+    e2 = timed_leg(sb, variant, args.steps, args.warmup, e2e=True)
     id_bytes = 4 * g.n_swap * 8
-    e2e = {"value": world * 2 * g.swap_bytes / (e2e_ms * 1e-3) / GB, "unit": "GB/s", "ms_per_step": e2e_ms,
+    e2e = {"value": e2["value"], "unit": "GB/s", "ms_per_step": e2["ms_per_step"],
            "h2d_bytes_per_step": g.swap_bytes + id_bytes, "d2h_bytes_per_step": g.swap_bytes + 4,
+           "verified": e2["all_verified"],
            "api": "PagedKVCache.swap_out/swap_in -> torch.ops.pcie_through.swap_out/swap_in; payload moves "
                   "between HBM and the pinned host pool inside the timed region"}
 
+    # ---- optional extra variants on the same state ---------------------------------------------
+    extra = {}
+    for var in [v for v in args.variants.split(",") if v]:
+        if var.startswith("staged"):   # "staged" or "staged:<lanes>"
+            lanes = int(var.split(":")[1]) if ":" in var else 0
+            lib.hfk_set_staged_copy_lanes(lanes)
+            sb.mover = "staged"
+            r = timed_leg(sb, variant, args.steps, args.warmup, e2e=False)
+            sb.mover = mover
+            lib.hfk_set_staged_copy_lanes(args.staged_lanes)
+        elif var.startswith("mover="):
+            sb.mover = {"vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK}[var.split("=")[1]]
+            r = timed_leg(sb, variant, args.steps, args.warmup, e2e=False)
+            sb.mover = mover
+        else:
+            r = timed_leg(sb, var, args.steps, args.warmup, e2e=False)
+        per = ctx.gather_floats([r["out_gbs"], r["in_gbs"]])
+        extra[var] = {"value": r["value"], "ms_per_step": r["ms_per_step"], "verified": r["all_verified"],
+                      "swap_out_GBps_per_rank": [round(p[0], 2) for p in per],
+                      "swap_in_GBps_per_rank": [round(p[1], 2) for p in per], "plan_rank0": r["plan"]}
+    beside = None
+    if args.beside_gemm and world == 1:
+        beside = bench_large_swap_beside_gemm(sb, device, min(args.steps, 5))
+
+    # ---- Llama-3-70B TP8 shard, short run on the same pinned buffer (every N) -------------------
+    config4 = None
+    del sb, cache
+    torch.cuda.empty_cache()
+    if not args.no_config4 and g.name == "llama3_8b_swap":
+        g4 = geometry("llama3_70b_tp8_swap")
+        slot4 = g4.layers * 2 * g4.block_bytes
+        slots4 = min(g4.host_slots, host_raw.numel() // slot4)
+        if slots4 >= 2 * g4.n_swap:
+            cache4 = PagedKVCache(g4.layers, g4.num_blocks, g4.block_size, g4.kv_heads, g4.head_dim, g4.dtype, device,
+                                  host_slots=slots4, host_raw=host_raw)
+            fill_random_bytes(cache4._k_store, 300 + rank)
+            fill_random_bytes(cache4._v_store, 400 + rank)
+            sb4 = SwapBench(g4, cache4, ctx, pkg, 4, mover, aiv, args.staging_mb)
+            r4 = timed_leg(sb4, variant, 3, 1, e2e=False)
+            per4 = ctx.gather_floats([r4["out_gbs"], r4["in_gbs"]])
+            config4 = {"workload": g4.name, "steps": 3, "warmup": 1, "value": r4["value"], "unit": "GB/s",
+                       "ms_per_step": r4["ms_per_step"], "bytes_per_direction_per_gpu": g4.swap_bytes,
+                       "swap_out_GBps_per_gpu_mean": statistics.mean(p[0] for p in per4),
+                       "swap_in_GBps_per_gpu_mean": statistics.mean(p[1] for p in per4),
+                       "swap_out_GBps_per_rank": [round(p[0], 2) for p in per4],
+                       "swap_in_GBps_per_rank": [round(p[1], 2) for p in per4],
+                       "host_slots": slots4, "device_blocks": g4.num_blocks, "variant": variant,
+                       "pool_note": "" if slots4 == g4.host_slots else
+                       f"host pool of {slots4} slots on the pinned buffer shared with the Llama-3-8B run "
+                       f"(configuration: {g4.host_slots}); transferred set unchanged",
+                       "verified": r4["all_verified"]}
+            del sb4, cache4
+            torch.cuda.empty_cache()
+
+    # ---- prefetch pipeline next to a GEMM, shipped defaults, short run (N = 1) --------------------
+    overlap = None
+    if world == 1 and not args.no_overlap and g.name == "llama3_8b_swap":
+        g5 = geometry("qwen2_7b_fp8_prefetch")
+        ob = OverlapBench(g5, device, pkg, host_raw=host_raw)
+        overlap = overlap_summary(ob, reps=args.overlap_reps, group=args.overlap_group or DEFAULT_PREFETCH_GROUP)
+        del ob
+        torch.cuda.empty_cache()
+
     # ---- gather leg (single-GPU runs) ------------------------------------------------------
-    host_pool_keepalive = cache  # noqa: F841
     gather = None
     if world == 1 and not args.no_gather and g.name != "tiny":
-        del cache, host_pool_keepalive, dev_sets
-        torch.cuda.empty_cache()
-        gather = bench_gather(device, max(args.steps, 5), args.warmup, mover,
+        gather = bench_gather(device, max(args.steps, 5), args.warmup, mover if mover != "staged" else None,
                               args.gather_aiv if args.gather_aiv > 0 else None)
 
     if rank != 0:
@@ -786,54 +1221,95 @@ def main() -> None:
         pass
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
     hbm_src = "MEASURED_PEAKS.json hbm_gbs (of measured)" if peaks else "6650 GB/s (of fallback)"
-    out_gbs = g.swap_bytes / (statistics.mean(out_ms) * 1e-3) / GB
-    in_gbs = g.swap_bytes / (statistics.mean(in_ms) * 1e-3) / GB
-    achieved = 2 * g.swap_bytes / ((statistics.mean(out_ms) + statistics.mean(in_ms)) * 1e-3) / GB
+    out_gbs, in_gbs = val["out_gbs"], val["in_gbs"]
+    achieved = 2 * g.swap_bytes / ((statistics.mean(val["out_ms"]) + statistics.mean(val["in_ms"])) * 1e-3) / GB
     pcie_peak = (pcie["h2d"] + pcie["d2h"]) / 2
+    ratio, ratio_src = traffic_ratio("kv_swap_kernel", 1.0097)
     roofline = {"bound": "pcie", "kernel": "kv_swap_*_kernel (swap-out and swap-in launches)",
                 "achieved": achieved, "peak": pcie_peak, "unit": "GB/s", "frac": achieved / pcie_peak,
-                "traffic": int(1.0841e9 * g.swap_bytes / 1073741824),
-                "traffic_source": "dram__bytes_read+write of one ncu capture of the swap-out launch at this step size "
-                                  "(1.0769 GB read + 0.0072 GB written per 1.0737 GB moved), scaled by bytes moved",
+                "traffic": int(ratio * g.swap_bytes), "traffic_source": ratio_src,
                 "peak_source": "live cudaMemcpyAsync of 1 GiB pinned<->device, best of 5, mean of the two "
                                "directions (MEASURED_PEAKS.json holds no PCIe figure)",
-                "swap_out": {"achieved": out_gbs, "peak": pcie["d2h"], "frac": out_gbs / pcie["d2h"]},
-                "swap_in": {"achieved": in_gbs, "peak": pcie["h2d"], "frac": in_gbs / pcie["h2d"]},
-                "nominal_gen5_x16": 63.0, "algorithmic_bytes_per_launch": g.swap_bytes}
+                "swap_out_achieved": out_gbs, "swap_out_peak": pcie["d2h"], "swap_out_frac": out_gbs / pcie["d2h"],
+                "swap_in_achieved": in_gbs, "swap_in_peak": pcie["h2d"], "swap_in_frac": in_gbs / pcie["h2d"],
+                "nominal_gen5_x16": 63.0, "algorithmic_bytes_per_launch": g.swap_bytes,
+                "verified": bool(val["all_verified"] and e2["all_verified"])}
     if pcie_conc is not None:
         # N > 1: what the host gives N links at once is the meaningful denominator
         agg_out = sum(r[1] for r in per_rank)
         agg_in = sum(r[2] for r in per_rank)
-        conc_d2h = sum(r[1] for r in pcie_conc)
         conc_h2d = sum(r[0] for r in pcie_conc)
-        roofline["all_ranks_concurrent"] = {
-            "swap_out_aggregate": agg_out, "memcpy_d2h_aggregate": conc_d2h, "frac_out": agg_out / conc_d2h,
-            "swap_in_aggregate": agg_in, "memcpy_h2d_aggregate": conc_h2d, "frac_in": agg_in / conc_h2d,
-            "note": "cudaMemcpyAsync with every rank copying at once (8 x 1 GiB per direction after a barrier); "
-                    "roofline.peak above is one link alone"}
-    line = {"metric": "kv_swap_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        conc_d2h = sum(r[1] for r in pcie_conc)
+        conc_bidir = sum(r[2] for r in pcie_conc)
+        roofline.update({
+            "swap_out_aggregate": agg_out, "swap_in_aggregate": agg_in,
+            "concurrent_d2h_aggregate": conc_d2h, "concurrent_h2d_aggregate": conc_h2d,
+            "concurrent_bidir_aggregate": conc_bidir,
+            "frac_out_vs_concurrent": agg_out / conc_d2h, "frac_in_vs_concurrent": agg_in / conc_h2d,
+            "frac_vs_concurrent_bidir": val["value"] / conc_bidir,
+            "concurrent_note": "cudaMemcpyAsync with every rank copying at once: one direction (8 x 1 GiB) and both "
+                               "directions on two streams (4 + 4 x 1 GiB, both directions' bytes over the time "
+                               "until both are done); roofline.peak is one link alone"})
+    if config4 is not None:
+        roofline.update({"config4_value": config4["value"], "config4_ms_per_step": config4["ms_per_step"],
+                         "config4_swap_out_GBps_per_gpu": config4["swap_out_GBps_per_gpu_mean"],
+                         "config4_swap_in_GBps_per_gpu": config4["swap_in_GBps_per_gpu_mean"],
+                         "config4_verified": config4["verified"]})
+    if overlap is not None:
+        roofline.update({"overlap_gemm_slowdown_pct": overlap["gemm_slowdown_pct"],
+                         "overlap_swap_in_gbs": overlap["swap_in_gbs"], "overlap_swap_out_gbs": overlap["swap_out_gbs"],
+                         "overlap_swap_in_gbs_no_gemm": overlap["swap_in_gbs_no_gemm"],
+                         "overlap_swap_out_gbs_no_gemm": overlap["swap_out_gbs_no_gemm"],
+                         "overlap_gemm_tflops": overlap["gemm_tflops"], "overlap_verified": overlap["verified"]})
+    line = {"metric": "kv_swap_GBps", "value": val["value"], "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": val["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "u8", "data": "synthetic", "config": config,
-            "per_gpu": value / world, "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline,
-            "clocks": clocks, "status_word": status, "mover": args.mover, "aiv": args.aiv or "default",
-            "pcie_memcpy_peak": pcie,
+            "per_gpu": val["value"] / world, "e2e": e2e, "gpu_launches": launches_value, "roofline": roofline,
+            "verified": roofline["verified"], "clocks": clocks, "status_word": val["status"] | e2["status"],
+            "mover": args.mover, "aiv": args.aiv or "default", "pcie_memcpy_peak": pcie,
+            "verify": {"what": "after each timed leg, the last step's host slots against their source blocks and the "
+                               "swapped-in blocks against their slots, every layer, K and V, on every rank; plus "
+                               "the CPU oracle on a sample", "bytes_checked_rank0": val["verify"]["bytes_checked"],
+                       "mismatches_rank0": val["verify"]["mismatches"]},
             "pcie_memcpy_concurrent_per_rank": None if pcie_conc is None else
-            [{"rank": i, "h2d": r[0], "d2h": r[1]} for i, r in enumerate(pcie_conc)],
+            [{"rank": i, "h2d": r[0], "d2h": r[1], "bidir_total": r[2]} for i, r in enumerate(pcie_conc)],
             "per_rank": [{"rank": i, "numa_node": int(r[0]), "pci_bus": "%02x" % int(r[4]), "swap_out_GBps": r[1],
-                          "swap_in_GBps": r[2], "ms_per_step": r[3]} for i, r in enumerate(per_rank)],
+                          "swap_in_GBps": r[2], "ms_per_step": r[3], "verified": bool(r[5])}
+                         for i, r in enumerate(per_rank)],
             "host": {"cpus": os.cpu_count(), "mem_available_GB": round(mem_available_bytes() / 1e9, 1)}}
+    if extra:
+        line["variants"] = extra
+    if beside is not None:
+        line["beside_gemm"] = beside
+    if config4 is not None:
+        line["config4"] = config4
+    if overlap is not None:
+        line["overlap"] = overlap
     if gather is not None:
+        gr, gsrc = traffic_ratio("paged_gather_kernel", 0.9957)
         gather["roofline"] = {"bound": "hbm", "kernel": "paged_gather_*_kernel", "achieved": gather["value"],
                               "peak": hbm_peak, "unit": "GB/s", "frac": gather["value"] / hbm_peak,
-                              "traffic": int(0.9957 * gather["algorithmic_bytes"]),
-                              "traffic_source": "one ncu capture of an 8-sequence batch (10.241 GB DRAM read+write for "
-                                                "10.285 GB algorithmic), scaled by the tokens gathered",
+                              "traffic": int(gr * gather["algorithmic_bytes"]), "traffic_source": gsrc,
                               "peak_source": hbm_src, "nominal": 8000.0}
+        roofline.update({"gather_achieved": gather["value"], "gather_frac_of_hbm": gather["value"] / hbm_peak,
+                         "gather_verified": gather["verified"]})
         line["gather"] = gather
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_swap(g, 10, 1)
     print(json.dumps(line), flush=True)
     ctx.close()
+
+
+# How a step is issued when several ranks share the host (see SwapBench); chosen by measurement.
+MULTI_GPU_VARIANT = "stagger"
+# Layers per launch of the prefetch pipeline in the default line's `overlap` run.
+DEFAULT_PREFETCH_GROUP = 1
+VARIANT_TEXT = {
+    "sequential": "swap-out then swap-in of the same slots, one stream",
+    "stagger": "odd ranks swap-in (the previous step's slots) first, even ranks swap-out first",
+    "bidir": "swap-out and swap-in (the previous step's slots) concurrently on two streams per rank",
+    "interleave": "each step cut into k parts, swap-out and swap-in parts alternating; odd ranks start with swap-in",
+}
 
 
 if __name__ == "__main__":

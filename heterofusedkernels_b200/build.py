@@ -33,7 +33,7 @@ INCLUDE = ROOT / "include"
 
 CAPI_SOURCES = ["hfk_capi.cu", "host_registry.cpp"]
 CAPI_DEPS = ["common.cuh", "kv_swap.cuh", "paged_gather.cuh", "row_gather.cuh", "block_transfer.cuh", "relayout_swap.cuh",
-             "host_util.h"]
+             "kv_migrate.cuh", "ptr_check.h", "host_util.h"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -27,6 +27,7 @@ HFK_DEV_BAD_HOST_SLOT_ID = 0x2
 HFK_DEV_BAD_ROW_ID = 0x4
 HFK_DEV_BAD_SEQ_LEN = 0x8
 HFK_DEV_WAIT_TIMEOUT = 0x10
+HFK_DEV_BAD_LAYER_PTR = 0x20
 
 MOVER_AUTO, MOVER_VECTOR, MOVER_BULK = 0, 1, 2
 HFK_MAX_SEQS = 1024
@@ -74,6 +75,26 @@ class RelayoutDesc(C.Structure):
     ]
 
 
+class MigrateDesc(C.Structure):
+    """struct hfk_migrate_desc"""
+    _fields_ = [
+        ("src_k_layer_ptrs", C.c_void_p),
+        ("src_v_layer_ptrs", C.c_void_p),
+        ("dst_k_layer_ptrs", C.c_void_p),
+        ("dst_v_layer_ptrs", C.c_void_p),
+        ("src_block_ids", C.c_void_p),
+        ("dst_block_ids", C.c_void_p),
+        ("ids_are_int64", C.c_int),
+        ("layers", C.c_int),
+        ("n_blocks", C.c_int64),
+        ("block_bytes", C.c_int64),
+        ("src_block_stride", C.c_int64),
+        ("dst_block_stride", C.c_int64),
+        ("num_src_blocks", C.c_int64),
+        ("num_dst_blocks", C.c_int64),
+    ]
+
+
 class PagedGatherDesc(C.Structure):
     """struct hfk_paged_gather_desc"""
     _fields_ = [
@@ -108,6 +129,12 @@ PROTOTYPES = {
     "hfk_set_bulk_lag": (C.c_int, [C.c_int]),
     "hfk_set_vector_geometry": (C.c_int, [C.c_int, C.c_int]),
     "hfk_set_gather_tuning": (C.c_int, [C.c_int, C.c_int]),
+    "hfk_set_staged_copy_lanes": (C.c_int, [C.c_int]),
+    "hfk_debug_set_stamps": (C.c_int, [C.c_void_p, C.c_size_t]),
+    "hfk_debug_stamp_marker": (C.c_int, [C.c_void_p]),
+    "hfk_migrate_blocks": (C.c_int, [C.POINTER(MigrateDesc), C.c_int, C.c_void_p]),
+    "hfk_migrate_blocks_copy_engine": (C.c_int, [C.POINTER(MigrateDesc), C.c_int, C.c_int, C.c_void_p]),
+    "hfk_enable_peer_access": (C.c_int, [C.c_int]),
     "hfk_register_ptr": (C.c_void_p, [C.c_void_p, C.c_size_t]),
     "hfk_unregister_ptr": (C.c_int, [C.c_void_p]),
     "hfk_get_device_ptr": (C.c_size_t, [C.c_size_t]),

@@ -6,15 +6,102 @@ per-layer pointer table once on the CPU and move it to the device
 ``memory.alloc_numa_pinned_tensor`` (:28-34) and alternate streams per transfer
 (:50-72).  ``PagedKVCache`` holds exactly that state for a vLLM-style cache —
 per layer one K and one V tensor ``[num_blocks, block_size, kv_heads, head_dim]``
-— and forwards to ``torch.ops.pcie_through.*``.
+— plus a free list of host slots, and forwards to ``torch.ops.pcie_through.*``.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+import bisect
+from typing import Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 
 import heterofusedkernels_b200 as _pkg
+
+
+class HostSlotPool:
+    """Free list of host slots that hands out *runs* of consecutive slots when it can.
+
+    A swapped-out block occupies one slot of the pinned pool until it is swapped in again
+    (the reference test's pool is such an array of block slots, test_transfer_kernel.py:28-34).
+    Consecutive slots are contiguous in host memory, so a request served by one run lets the
+    staged mover cross the link with a few large copy-engine transfers instead of one per slot.
+
+    ``alloc(n)`` takes the smallest free run that holds n slots; when no run is long enough it
+    takes the longest runs first.  ``free(slots)`` returns slots and merges neighbouring runs.
+    """
+
+    def __init__(self, num_slots: int):
+        self.num_slots = int(num_slots)
+        self._starts: List[int] = [0] if num_slots > 0 else []   # sorted starts of the free runs
+        self._len: Dict[int, int] = {0: self.num_slots} if num_slots > 0 else {}
+        self.free_count = self.num_slots
+
+    def largest_run(self) -> int:
+        return max(self._len.values(), default=0)
+
+    def runs(self) -> List[Tuple[int, int]]:
+        """Free runs as (first slot, length), in slot order."""
+        return [(s, self._len[s]) for s in self._starts]
+
+    def _take(self, start: int, n: int) -> range:
+        length = self._len.pop(start)
+        i = bisect.bisect_left(self._starts, start)
+        del self._starts[i]
+        if length > n:
+            self._starts.insert(i, start + n)
+            self._len[start + n] = length - n
+        self.free_count -= n
+        return range(start, start + n)
+
+    def alloc(self, n: int) -> torch.Tensor:
+        """n distinct free slots as an int64 CPU tensor; raises when fewer than n are free."""
+        if n < 0 or n > self.free_count:
+            raise RuntimeError(f"host pool exhausted: {n} slots wanted, {self.free_count} free")
+        if n == 0:
+            return torch.empty(0, dtype=torch.int64)
+        fits = [s for s in self._starts if self._len[s] >= n]
+        if fits:
+            best = min(fits, key=lambda s: (self._len[s], s))
+            return torch.tensor(list(self._take(best, n)), dtype=torch.int64)
+        out: List[int] = []
+        for start in sorted(self._starts, key=lambda s: (-self._len[s], s)):
+            take = min(self._len[start], n - len(out))
+            out.extend(self._take(start, take))
+            if len(out) == n:
+                break
+        return torch.tensor(out, dtype=torch.int64)
+
+    def free(self, slots) -> None:
+        ids = sorted(int(x) for x in (slots.tolist() if torch.is_tensor(slots) else slots))
+        i = 0
+        while i < len(ids):
+            j = i
+            while j + 1 < len(ids) and ids[j + 1] == ids[j] + 1:
+                j += 1
+            self._insert_run(ids[i], j - i + 1)
+            i = j + 1
+
+    def _insert_run(self, start: int, n: int) -> None:
+        if start < 0 or start + n > self.num_slots:
+            raise ValueError(f"slots {start}..{start + n - 1} are outside the pool")
+        i = bisect.bisect_left(self._starts, start)
+        prev = self._starts[i - 1] if i > 0 else None
+        nxt = self._starts[i] if i < len(self._starts) else None
+        if (prev is not None and prev + self._len[prev] > start) or (nxt is not None and start + n > nxt):
+            raise ValueError(f"slots {start}..{start + n - 1} are already free")
+        self.free_count += n
+        if prev is not None and prev + self._len[prev] == start:      # merge with the run before
+            start, n = prev, n + self._len.pop(prev)
+            i -= 1
+            del self._starts[i]
+        if nxt is not None and start + n == nxt:                        # and with the run after
+            n += self._len.pop(nxt)
+            del self._starts[i]
+        self._starts.insert(i, start)
+        self._len[start] = n
+
+
+MoverArg = Union[None, int, str]
 
 
 class PagedKVCache:
@@ -23,12 +110,17 @@ class PagedKVCache:
     Host pool layout: ``[host_slots, layers, 2, block_size, kv_heads, head_dim]`` —
     one slot holds every layer's K and V of a block contiguously, like the
     reference's host block that holds all layers (test_transfer_kernel.py:28).
+
+    ``swap_out`` / ``swap_in`` take ``mover`` = one of ``capi.MOVER_*`` (a kernel crosses the
+    link) or ``"staged"`` (a packing kernel plus copy-engine transfers; needs the slot ids on
+    the host, which is where a scheduler has them).
     """
 
     def __init__(self, layers: int, num_blocks: int, block_size: int, kv_heads: int, head_dim: int,
                  dtype: torch.dtype, device: torch.device | str = "cuda", host_slots: int = 0,
                  k_caches: Optional[Sequence[torch.Tensor]] = None,
-                 v_caches: Optional[Sequence[torch.Tensor]] = None):
+                 v_caches: Optional[Sequence[torch.Tensor]] = None,
+                 host_raw: Optional[torch.Tensor] = None):
         _pkg.load_ops()
         self.layers, self.num_blocks, self.block_size = layers, num_blocks, block_size
         self.kv_heads, self.head_dim, self.dtype = kv_heads, head_dim, dtype
@@ -52,20 +144,35 @@ class PagedKVCache:
         self.elt = self.k_caches[0].element_size()
         self.token_bytes = kv_heads * head_dim * self.elt
         self.block_bytes = block_size * self.token_bytes
-        self.host_slots = host_slots
+        self.slot_bytes = layers * 2 * self.block_bytes
+        self.host_slots = 0
         self.host_pool: Optional[torch.Tensor] = None
         self._host_raw: Optional[torch.Tensor] = None
-        if host_slots > 0:
+        self.slot_pool: Optional[HostSlotPool] = None
+        self._staging_buf: Optional[torch.Tensor] = None
+        if host_raw is not None:
+            self.attach_host_raw(host_raw, host_slots)
+        elif host_slots > 0:
             self.attach_host_pool(host_slots)
 
     # -- host pool -------------------------------------------------------------
     def attach_host_pool(self, host_slots: int) -> torch.Tensor:
         with torch.cuda.device(self.device):
-            raw = _pkg.memory.alloc_numa_pinned_tensor(host_slots * self.layers * 2 * self.block_bytes)
+            raw = _pkg.memory.alloc_numa_pinned_tensor(host_slots * self.slot_bytes)
+        return self.attach_host_raw(raw, host_slots)
+
+    def attach_host_raw(self, raw: torch.Tensor, host_slots: int = 0) -> torch.Tensor:
+        """Uses (a prefix of) an existing registered byte buffer — e.g. one obtained from
+        ``memory.alloc_numa_pinned_tensor`` and shared by several caches in turn — as the pool."""
+        fit = raw.numel() * raw.element_size() // self.slot_bytes
+        host_slots = fit if host_slots <= 0 else host_slots
+        assert 0 < host_slots <= fit, "the byte buffer is smaller than the pool asked for"
         self._host_raw = raw
         self.host_slots = host_slots
-        self.host_pool = raw.view(self.dtype).view(host_slots, self.layers, 2, self.block_size,
-                                                   self.kv_heads, self.head_dim)
+        flat = raw.view(torch.uint8)[:host_slots * self.slot_bytes]
+        self.host_pool = flat.view(self.dtype).view(host_slots, self.layers, 2, self.block_size,
+                                                    self.kv_heads, self.head_dim)
+        self.slot_pool = HostSlotPool(host_slots)
         return self.host_pool
 
     def swap_bytes(self, n_blocks: int) -> int:
@@ -77,29 +184,56 @@ class PagedKVCache:
             ids = torch.tensor(list(ids), dtype=torch.int64)
         return ids.to(self.device, non_blocking=True)
 
-    def swap_out(self, device_block_ids, host_slot_ids, aiv: Optional[int] = None,
-                 mover: Optional[int] = None) -> None:
-        """host_pool[slot] <- cache[block], every layer, K and V, one launch, current stream."""
-        torch.ops.pcie_through.swap_out(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
-                                        self._ids(host_slot_ids), self.num_blocks, None, aiv, mover)
+    @staticmethod
+    def _cpu_ids(ids) -> torch.Tensor:
+        if not torch.is_tensor(ids):
+            ids = torch.tensor(list(ids), dtype=torch.int64)
+        return ids if ids.device.type == "cpu" else ids.cpu()
+
+    def swap_out(self, device_block_ids, host_slot_ids=None, aiv: Optional[int] = None,
+                 mover: MoverArg = None) -> torch.Tensor:
+        """host_pool[slot] <- cache[block], every layer, K and V, one call, current stream.
+
+        Without ``host_slot_ids`` the slots come from the free list (``self.slot_pool``), as runs of
+        consecutive slots where possible; the slots used are returned (give them back with
+        ``release`` once the blocks have been swapped in again or dropped)."""
+        n = len(device_block_ids)
+        if host_slot_ids is None:
+            host_slot_ids = self.slot_pool.alloc(n)
+        if mover == "staged":
+            self.swap_out_staged(device_block_ids, self._cpu_ids(host_slot_ids), aiv=aiv)
+        else:
+            torch.ops.pcie_through.swap_out(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
+                                            self._ids(host_slot_ids), self.num_blocks, None, aiv, mover)
+        return host_slot_ids
 
     def swap_in(self, device_block_ids, host_slot_ids, aiv: Optional[int] = None,
-                mover: Optional[int] = None) -> None:
-        """cache[block] <- host_pool[slot], every layer, K and V, one launch, current stream."""
-        torch.ops.pcie_through.swap_in(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
-                                       self._ids(host_slot_ids), self.num_blocks, None, aiv, mover)
+                mover: MoverArg = None, release: bool = False) -> None:
+        """cache[block] <- host_pool[slot], every layer, K and V, one call, current stream.
+        ``release=True`` returns the slots to the free list (the copy is only enqueued: do not
+        swap out into them again from another stream before it has run)."""
+        if mover == "staged":
+            self.swap_in_staged(device_block_ids, self._cpu_ids(host_slot_ids), aiv=aiv)
+        else:
+            torch.ops.pcie_through.swap_in(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
+                                           self._ids(host_slot_ids), self.num_blocks, None, aiv, mover)
+        if release:
+            self.release(host_slot_ids)
+
+    def release(self, host_slot_ids) -> None:
+        self.slot_pool.free(self._cpu_ids(host_slot_ids))
 
     def _staging(self, staging_bytes: int) -> torch.Tensor:
-        slot = self.layers * 2 * self.block_bytes
-        want = max(slot, staging_bytes)
-        if getattr(self, "_staging_buf", None) is None or self._staging_buf.numel() < want:
+        want = max(self.slot_bytes, staging_bytes)
+        if self._staging_buf is None or self._staging_buf.numel() < want:
             self._staging_buf = torch.empty(want, dtype=torch.uint8, device=self.device)
         return self._staging_buf
 
     def swap_out_staged(self, device_block_ids, host_slot_ids_cpu: torch.Tensor, staging_bytes: int = 256 << 20,
                         aiv: Optional[int] = None) -> None:
         """Swap-out through the copy engine: a packing kernel into a staging buffer, then one
-        cudaMemcpyAsync per host slot (256-byte PCIe transactions instead of a kernel's 128-byte ones)."""
+        cudaMemcpyAsync per run of consecutive host slots (256-byte PCIe transactions instead of a
+        kernel's 128-byte ones)."""
         torch.ops.pcie_through.swap_out_staged(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
                                                host_slot_ids_cpu, self._staging(staging_bytes), self.num_blocks,
                                                None, aiv)
@@ -134,23 +268,60 @@ class PagedKVCache:
                                             self.block_size, self.num_blocks, None, aiv, mover)
         return k_out, v_out
 
+    def migrate_to(self, other: "PagedKVCache", src_block_ids, dst_block_ids, aiv: Optional[int] = None,
+                   run_on: str = "dst") -> None:
+        """other.cache[dst_block] <- self.cache[src_block], every layer, K and V, one launch.
+
+        ``other`` may be this cache (a copy between blocks), another cache on the same GPU, or a
+        cache on a peer GPU; then one side of each copy crosses NVLink.  ``run_on`` picks the GPU that
+        runs the kernel: "dst" pulls (peer loads), "src" pushes (peer stores).  The launch goes to the
+        current stream of that GPU."""
+        assert other.layers == self.layers and other.block_bytes == self.block_bytes
+        dev = other.device if run_on == "dst" else self.device
+        if dev != self.device or dev != other.device:
+            with torch.cuda.device(dev):
+                peer = self.device if dev == other.device else other.device
+                _pkg.capi.check(_pkg.capi.lib().hfk_enable_peer_access(peer.index), "hfk_enable_peer_access")
+        tabs = [t.to(dev) for t in (self.k_ptrs_cpu, self.v_ptrs_cpu, other.k_ptrs_cpu, other.v_ptrs_cpu)]
+        src = (src_block_ids if torch.is_tensor(src_block_ids) else torch.tensor(list(src_block_ids))).to(dev)
+        dst = (dst_block_ids if torch.is_tensor(dst_block_ids) else torch.tensor(list(dst_block_ids))).to(dev)
+        with torch.cuda.device(dev):
+            torch.ops.pcie_through.migrate_blocks(tabs[0], tabs[1], tabs[2], tabs[3], src, dst, self.block_bytes,
+                                                  self.num_blocks, other.num_blocks, None, None, aiv)
+
     def status(self) -> int:
-        """Reads and clears the device status word (bits HFK_DEV_* of hfk_b200.h)."""
+        """Reads and clears the device status word (bits HFK_DEV_* of hfk_b200.h).  The word is per
+        GPU, not per cache or stream: quiesce side streams first."""
         with torch.cuda.device(self.device):
             return int(torch.ops.pcie_through.device_status())
 
 
+LayerArg = Union[int, Tuple[int, int], range]
+
+
 class LayerwisePrefetcher:
     """Layer-wise prefetch pipeline: while layer l computes on the caller's stream,
-    the blocks of layer l+1 are swapped in on a side stream and other blocks are
-    swapped out on a second one; events order the swap before the layer that needs it.
+    the blocks of the next layer(s) are swapped in on a side stream and other blocks are
+    swapped out on a second one.
 
-    One single-layer view of the cache is made per layer (pointer tables of length 1),
-    so each call moves only that layer's K and V.
+    Ordering.  A swap on a side stream starts only after the work the caller had already enqueued
+    on its own stream (``after=None``: the side stream waits for the caller's current stream at the
+    moment of the call; pass an event to wait for exactly that, or ``False`` to take over the ordering
+    yourself).  So an ``evict`` issued right after the kernel that wrote the blocks reads finished
+    blocks, and a ``prefetch`` cannot overwrite blocks an earlier kernel still reads.  In the other
+    direction ``wait(layer)`` makes the caller's stream wait for that layer's swap-in, and
+    ``wait_evicted(layer)`` for its swap-out (before the blocks are reused).  Id tensors are kept alive
+    for the side stream (``record_stream``).
+
+    Layers.  ``layer`` is one index or a range ``(first, last_exclusive)``: a range moves several
+    layers in one launch through slices of the pointer tables and of the pool, which amortises the
+    launch cost of these small (a few MB) transfers; the events of every layer of the range are
+    recorded after the launch.
 
     Defaults: the vector mover with 16 CTAs per direction.  Measured next to a bf16 GEMM that fills
     the device, both directions then run at 41-44 GB/s with the GEMM 2-5 % slower, while the bulk
-    mover with 8 or more single-warp CTAs drops to about 18 GB/s per direction.
+    mover's single-warp CTAs need most of an SM's shared memory for their ring and have to wait
+    for GEMM CTAs to retire.
     """
     DEFAULT_AIV = 16
     DEFAULT_MOVER = _pkg.capi.MOVER_VECTOR
@@ -159,28 +330,81 @@ class LayerwisePrefetcher:
         self.cache = cache
         self.in_stream = torch.cuda.Stream(device=cache.device, priority=-1)
         self.out_stream = torch.cuda.Stream(device=cache.device, priority=-1)
-        self.k_ptrs = [cache.k_ptrs[l:l + 1] for l in range(cache.layers)]
-        self.v_ptrs = [cache.v_ptrs[l:l + 1] for l in range(cache.layers)]
-        self.pools = [cache.host_pool[:, l:l + 1] for l in range(cache.layers)]
         self.ready = [torch.cuda.Event() for _ in range(cache.layers)]
+        self.evicted = [torch.cuda.Event() for _ in range(cache.layers)]
+        self._views: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
 
-    def prefetch(self, layer: int, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor,
-                 aiv: Optional[int] = None, mover: Optional[int] = None) -> torch.cuda.Event:
-        c = self.cache
+    def _span(self, layer: LayerArg) -> Tuple[int, int]:
+        if isinstance(layer, int):
+            first, last = layer, layer + 1
+        elif isinstance(layer, range):
+            assert layer.step == 1
+            first, last = layer.start, layer.stop
+        else:
+            first, last = layer
+        assert 0 <= first < last <= self.cache.layers, f"layer range {first}:{last} outside the cache"
+        return first, last
+
+    def _view(self, first: int, last: int):
+        """Pointer-table and pool slices of layers [first, last): a cache of last-first layers."""
+        key = (first, last)
+        if key not in self._views:
+            c = self.cache
+            self._views[key] = (c.k_ptrs[first:last], c.v_ptrs[first:last], c.host_pool[:, first:last])
+        return self._views[key]
+
+    def _order(self, side: torch.cuda.Stream, after) -> None:
+        if after is None:
+            side.wait_stream(torch.cuda.current_stream(self.cache.device))
+        elif after is not False:
+            side.wait_event(after)
+
+    def prefetch(self, layer: LayerArg, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor,
+                 aiv: Optional[int] = None, mover: Optional[int] = None, after=None) -> torch.cuda.Event:
+        """Swap-in of the listed blocks of ``layer`` (an index or a range) on the swap-in stream.
+        Returns the event of the last layer of the range."""
+        first, last = self._span(layer)
+        k_ptrs, v_ptrs, pool = self._view(first, last)
+        self._order(self.in_stream, after)
         with torch.cuda.stream(self.in_stream):
-            torch.ops.pcie_through.swap_in(self.k_ptrs[layer], self.v_ptrs[layer], self.pools[layer],
-                                           device_block_ids, host_slot_ids, c.num_blocks, None,
-                                           aiv or self.DEFAULT_AIV, mover or self.DEFAULT_MOVER)
-            self.ready[layer].record()
-        return self.ready[layer]
+            torch.ops.pcie_through.swap_in(k_ptrs, v_ptrs, pool, device_block_ids, host_slot_ids,
+                                           self.cache.num_blocks, None,
+                                           self.DEFAULT_AIV if aiv is None else aiv,
+                                           self.DEFAULT_MOVER if mover is None else mover)
+            for l in range(first, last):
+                self.ready[l].record()
+        device_block_ids.record_stream(self.in_stream)
+        host_slot_ids.record_stream(self.in_stream)
+        return self.ready[last - 1]
 
-    def evict(self, layer: int, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor,
-              aiv: Optional[int] = None, mover: Optional[int] = None) -> None:
-        c = self.cache
+    def evict(self, layer: LayerArg, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor,
+              aiv: Optional[int] = None, mover: Optional[int] = None, after=None) -> torch.cuda.Event:
+        """Swap-out of the listed blocks of ``layer`` (an index or a range) on the swap-out stream.
+        Returns the event to wait for before the blocks are reused."""
+        first, last = self._span(layer)
+        k_ptrs, v_ptrs, pool = self._view(first, last)
+        self._order(self.out_stream, after)
         with torch.cuda.stream(self.out_stream):
-            torch.ops.pcie_through.swap_out(self.k_ptrs[layer], self.v_ptrs[layer], self.pools[layer],
-                                            device_block_ids, host_slot_ids, c.num_blocks, None,
-                                            aiv or self.DEFAULT_AIV, mover or self.DEFAULT_MOVER)
+            torch.ops.pcie_through.swap_out(k_ptrs, v_ptrs, pool, device_block_ids, host_slot_ids,
+                                            self.cache.num_blocks, None,
+                                            self.DEFAULT_AIV if aiv is None else aiv,
+                                            self.DEFAULT_MOVER if mover is None else mover)
+            for l in range(first, last):
+                self.evicted[l].record()
+        device_block_ids.record_stream(self.out_stream)
+        host_slot_ids.record_stream(self.out_stream)
+        return self.evicted[last - 1]
 
     def wait(self, layer: int) -> None:
+        """The caller's stream waits until ``layer``'s swap-in has finished."""
         torch.cuda.current_stream(self.cache.device).wait_event(self.ready[layer])
+
+    def wait_evicted(self, layer: int) -> None:
+        """The caller's stream waits until ``layer``'s swap-out has read its blocks."""
+        torch.cuda.current_stream(self.cache.device).wait_event(self.evicted[layer])
+
+    def quiesce(self) -> None:
+        """The caller's stream waits for both side streams (e.g. before reading the status word)."""
+        cur = torch.cuda.current_stream(self.cache.device)
+        cur.wait_stream(self.in_stream)
+        cur.wait_stream(self.out_stream)

@@ -28,8 +28,15 @@ template <int kThreads, int kUnroll>
 __global__ void __launch_bounds__(kThreads) block_transfer_kernel(TransferArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char **lp = reinterpret_cast<unsigned char **>(smem_raw);
-  for (int l = threadIdx.x; l < a.layers; l += kThreads)
-    lp[l] = static_cast<unsigned char *>(a.layer_ptrs[l]);
+  // a null or misaligned layer base is reported and its vectors are skipped
+  for (int l = threadIdx.x; l < a.layers; l += kThreads) {
+    void *p = a.layer_ptrs[l];
+    if (!layer_ptr_ok(p)) {
+      raise_status(HFK_DEV_BAD_LAYER_PTR);
+      p = nullptr;
+    }
+    lp[l] = static_cast<unsigned char *>(p);
+  }
   __syncthreads();
   const int64_t total = a.block_size * a.layers * a.heads * a.d16;
   const int64_t stride = (int64_t)gridDim.x * kThreads;
@@ -41,17 +48,26 @@ __global__ void __launch_bounds__(kThreads) block_transfer_kernel(TransferArgs a
     r /= a.heads;
     const int64_t l = r % a.layers;
     const int64_t t = r / a.layers;
+    if (lp[l] == nullptr) return nullptr;
     return reinterpret_cast<uint4 *>(lp[l]) + (h * a.block_size + t) * a.d16 + dv;
   };
   int64_t v0 = (int64_t)blockIdx.x * kThreads + threadIdx.x;
   for (; v0 + (kUnroll - 1) * stride < total; v0 += kUnroll * stride) {
     uint4 x[kUnroll];
+    uint4 *dp[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) x[u] = ld_stream16(src + v0 + u * stride);
+    for (int u = 0; u < kUnroll; ++u) {
+      dp[u] = dst_of(v0 + u * stride);
+      if (dp[u]) x[u] = ld_stream16(src + v0 + u * stride);
+    }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) st_stream16(dst_of(v0 + u * stride), x[u]);
+    for (int u = 0; u < kUnroll; ++u)
+      if (dp[u]) st_stream16(dp[u], x[u]);
   }
-  for (; v0 < total; v0 += stride) st_stream16(dst_of(v0), ld_stream16(src + v0));
+  for (; v0 < total; v0 += stride) {
+    uint4 *dp = dst_of(v0);
+    if (dp) st_stream16(dp, ld_stream16(src + v0));
+  }
 }
 
 }  // namespace hfk

@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include "../../include/hfk_b200.h"
+#include "ptr_check.h"
 
 namespace hfk {
 
@@ -16,6 +17,47 @@ namespace hfk {
 __device__ unsigned int g_status_word;
 
 __device__ __forceinline__ void raise_status(unsigned int bit) { atomicOr(&g_status_word, bit); }
+
+// ---- optional per-CTA time stamps (diagnostics) ---------------------------
+// When a stamp buffer is installed (hfk_debug_set_stamps), thread 0 of every CTA of the data
+// movers appends one record {tag << 32 | SM id, CTA index, start ns, end ns} taken from
+// %globaltimer.  Word 0 of the buffer counts the records.  With no buffer installed the cost
+// is one load of a __device__ pointer per CTA.
+__device__ unsigned long long *g_stamp_buf;
+__device__ unsigned int g_stamp_cap;
+
+__device__ __forceinline__ unsigned int sm_id() {
+  unsigned int v;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(v));
+  return v;
+}
+__device__ __forceinline__ unsigned long long stamp_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+struct CtaStamp {
+  unsigned long long *rec;
+  __device__ __forceinline__ void begin(unsigned int tag) {
+    rec = nullptr;
+    if (threadIdx.x != 0) return;
+    unsigned long long *buf = g_stamp_buf;
+    if (buf == nullptr) return;
+    const unsigned long long i = atomicAdd(buf, 1ull);
+    if (i >= g_stamp_cap) return;
+    rec = buf + 1 + 4 * i;
+    rec[0] = ((unsigned long long)tag << 32) | sm_id();
+    rec[1] = blockIdx.x;
+    rec[2] = stamp_now();
+    rec[3] = 0;
+  }
+  __device__ __forceinline__ void end() {
+    if (threadIdx.x == 0 && rec != nullptr) rec[3] = stamp_now();
+  }
+};
+// tags of the stamp records
+constexpr unsigned int kStampMarker = 0, kStampSwapVector = 1, kStampSwapBulk = 2, kStampGatherBulk = 3,
+                       kStampGatherVector = 4, kStampMigrate = 5;
 
 // ---- 16-byte streaming accesses ------------------------------------------
 // Every byte on this path is touched exactly once, so both sides use the
@@ -182,8 +224,13 @@ struct PumpSmem {
 };
 
 // make_desc(k) returns the descriptor of this CTA's k-th unit, k < total.
+// Returns false when a bounded wait ran out: HFK_DEV_WAIT_TIMEOUT is raised, the loads that
+// were still in flight get one more (short) bounded wait each so that no copy is outstanding
+// into this CTA's shared memory when it exits, and the caller must stop issuing work.  After
+// a timeout the destination of the whole call is undefined.
+constexpr uint64_t kDrainLimitNs = 100000000ull;  // 0.1 s per stage that still has a load in flight
 template <int kPumpLag, typename MakeDesc>
-__device__ __forceinline__ void run_pump(PumpSmem *ps, unsigned char *stages, int stage_bytes,
+__device__ __forceinline__ bool run_pump(PumpSmem *ps, unsigned char *stages, int stage_bytes,
                                          int n_stages, int64_t total, uint32_t &seq,
                                          MakeDesc make_desc, int hints = 0) {
   // hints: bit 0 = loads carry an L2 evict-first policy, bit 1 = stores do
@@ -246,10 +293,20 @@ __device__ __forceinline__ void run_pump(PumpSmem *ps, unsigned char *stages, in
     if (lane == 0) bulk_commit();  // one group per unit, empty for skipped units
     ++done;
   }
-  if (!ok && lane == 0) raise_status(HFK_DEV_WAIT_TIMEOUT);
+  if (!ok && lane == 0) {
+    raise_status(HFK_DEV_WAIT_TIMEOUT);
+    // unit done-1 is the one that timed out; it and the units up to issued-1 may still have a
+    // load in flight
+    for (int64_t k = done - 1; k < issued; ++k) {
+      if (ps->desc[k & 63].bytes == 0) continue;
+      const uint32_t q = seq + (uint32_t)k;
+      mbar_wait_bounded(&ps->full[q % n_stages], (q / n_stages) & 1u, kDrainLimitNs);
+    }
+  }
   if (lane == 0) bulk_wait_all();
   seq += (uint32_t)total;
   __syncwarp();
+  return ok;
 }
 
 }  // namespace hfk

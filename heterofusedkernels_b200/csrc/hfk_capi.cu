@@ -12,12 +12,14 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 #include <string>
 #include <type_traits>
 
 #include "block_transfer.cuh"
 #include "common.cuh"
 #include "host_util.h"
+#include "kv_migrate.cuh"
 #include "kv_swap.cuh"
 #include "paged_gather.cuh"
 #include "relayout_swap.cuh"
@@ -41,9 +43,61 @@ int cuda_fail(cudaError_t e, const char *what) {
   return fail(HFK_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
 }
 
+// ---- status word ------------------------------------------------------------
+// hfk_device_status() snapshots the word with an atomic exchange into one of a few slots (one
+// per concurrent reader) and copies that slot back.
+constexpr unsigned int kStatusSnapshots = 64;
+__device__ unsigned int g_status_snapshot[kStatusSnapshots];
+std::atomic<unsigned int> g_status_ticket{0};
+__global__ void status_exchange_kernel(unsigned int slot) {
+  g_status_snapshot[slot] = atomicExch(&g_status_word, 0u);
+}
+
 // ---- tuning state ----------------------------------------------------------
 std::atomic<int> g_stage_bytes{0}, g_n_stages{0}, g_bulk_lag{0}, g_vec_threads{0}, g_vec_unroll{0};
 std::atomic<int> g_gather_hints{-1}, g_gather_blocked{-1};
+std::atomic<int> g_staged_lanes{0};
+
+// ---- copy lanes of the staged mover -------------------------------------------
+// The staged swap hands the link to the copy engines.  One stream executes its copies back to
+// back with a gap after each; B200 has several copy engines per direction, so the slot copies
+// are dealt round-robin to a few internal streams ("lanes") that fork from the caller's stream
+// and join it again (events), which keeps the link busy across the gaps.  Lanes and events are
+// created once per device on first use; a per-device mutex keeps two host threads from
+// interleaving their fork/join sequences on the shared events.
+constexpr int kMaxLanes = 4;
+constexpr int kMaxDevicesLanes = 64;
+struct CopyLanes {
+  std::mutex mu;
+  bool ready = false;
+  cudaStream_t lane[kMaxLanes];
+  cudaEvent_t fork;
+  cudaEvent_t join[kMaxLanes];
+};
+static CopyLanes g_lanes[kMaxDevicesLanes];
+
+static int lanes_for_current_device(CopyLanes **out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevicesLanes)
+    return fail(HFK_ERR_UNSUPPORTED, "staged swap: device ordinal %d beyond %d", dev, kMaxDevicesLanes);
+  CopyLanes *l = &g_lanes[dev];
+  std::lock_guard<std::mutex> g(l->mu);
+  if (!l->ready) {
+    for (int i = 0; i < kMaxLanes; ++i) {
+      if ((e = cudaStreamCreateWithFlags(&l->lane[i], cudaStreamNonBlocking)) != cudaSuccess)
+        return cuda_fail(e, "cudaStreamCreateWithFlags(copy lane)");
+      if ((e = cudaEventCreateWithFlags(&l->join[i], cudaEventDisableTiming)) != cudaSuccess)
+        return cuda_fail(e, "cudaEventCreateWithFlags(copy lane)");
+    }
+    if ((e = cudaEventCreateWithFlags(&l->fork, cudaEventDisableTiming)) != cudaSuccess)
+      return cuda_fail(e, "cudaEventCreateWithFlags(copy lane)");
+    l->ready = true;
+  }
+  *out = l;
+  return HFK_OK;
+}
 
 constexpr int kMaxDynSmem = 227 * 1024;
 
@@ -125,6 +179,16 @@ static int validate_swap(const hfk_swap_desc *d) {
     return fail(HFK_ERR_ALIGNMENT, "swap: block_bytes and all strides must be multiples of 16 bytes");
   if (!aligned16(d->host_pool)) return fail(HFK_ERR_ALIGNMENT, "swap: host pool is not 16-byte aligned");
   if (d->layers > 4096) return fail(HFK_ERR_TOO_LARGE, "swap: more than 4096 layers");
+  if (d->host_slot_stride < 0 || d->host_layer_stride < 0 || d->host_kv_stride < 0)
+    return fail(HFK_ERR_INVALID_ARG, "swap: negative host stride");
+  // chunks of the pool must not overlap: the strides have to nest around the chunk (an expanded
+  // or overlapping view of a pool would make distinct (slot, layer, K|V) chunks share bytes)
+  if (!strides_nest(d->block_bytes, {d->host_kv_stride, 2}, {d->host_layer_stride, d->layers},
+                    {d->host_slot_stride, d->num_host_slots}))
+    return fail(HFK_ERR_INVALID_ARG,
+                "swap: host strides (slot %lld, layer %lld, K|V %lld) let chunks of %lld bytes overlap",
+                (long long)d->host_slot_stride, (long long)d->host_layer_stride,
+                (long long)d->host_kv_stride, (long long)d->block_bytes);
   return HFK_OK;
 }
 
@@ -323,6 +387,9 @@ static int swap_staged_impl(const hfk_swap_desc *d, const void *slots_host, void
   if (d->host_kv_stride != d->block_bytes || d->host_layer_stride != 2 * d->block_bytes)
     return fail(HFK_ERR_UNSUPPORTED,
                 "swap_staged: the host pool must be slot-contiguous ([slot][layer][K|V][block])");
+  if (d->host_slot_stride < slot_bytes)
+    return fail(HFK_ERR_INVALID_ARG, "swap_staged: host_slot_stride %lld is smaller than one slot (%lld bytes)",
+                (long long)d->host_slot_stride, (long long)slot_bytes);
   if ((int64_t)staging_bytes < slot_bytes)
     return fail(HFK_ERR_TOO_LARGE, "swap_staged: staging buffer of %zu bytes holds less than one slot (%lld bytes)",
                 staging_bytes, (long long)slot_bytes);
@@ -338,6 +405,12 @@ static int swap_staged_impl(const hfk_swap_desc *d, const void *slots_host, void
   const int64_t per_round = (int64_t)(staging_bytes / (size_t)slot_bytes);
   const size_t id_width = d->ids_are_int64 ? 8 : 4;
   if (ctas <= 0) ctas = sm_count();  // the packing kernel is HBM to HBM: spread it over the device
+  int n_lanes = g_staged_lanes.load() > 0 ? g_staged_lanes.load() : kDefaultStagedLanes;
+  if (n_lanes > kMaxLanes) n_lanes = kMaxLanes;
+  CopyLanes *lanes = nullptr;
+  if (n_lanes > 1 && (rc = lanes_for_current_device(&lanes)) != HFK_OK) return rc;
+  std::unique_lock<std::mutex> lanes_guard;
+  if (lanes) lanes_guard = std::unique_lock<std::mutex>(lanes->mu);
   unsigned char *pool = static_cast<unsigned char *>(pool_host);
   unsigned char *stg = static_cast<unsigned char *>(staging);
   for (int64_t i0 = 0; i0 < d->n_blocks; i0 += per_round) {
@@ -370,19 +443,41 @@ static int swap_staged_impl(const hfk_swap_desc *d, const void *slots_host, void
     };
     cudaError_t e;
     if (to_host && (e = pack(true)) != cudaSuccess) return cuda_fail(e, "staging pack kernel");
-    // one copy-engine transfer per run of consecutive slots
+    // fork: the lanes start after everything enqueued on `stream` so far (the pack kernel, or
+    // for a swap-in whatever the caller ordered before this call)
+    if (lanes) {
+      if ((e = cudaEventRecord(lanes->fork, stream)) != cudaSuccess) return cuda_fail(e, "cudaEventRecord(fork)");
+      for (int q = 0; q < n_lanes; ++q)
+        if ((e = cudaStreamWaitEvent(lanes->lane[q], lanes->fork, 0)) != cudaSuccess)
+          return cuda_fail(e, "cudaStreamWaitEvent(fork)");
+    }
+    // one copy-engine transfer per run of consecutive slots; a long run is cut into pieces of at
+    // most kStagedMaxCopyBytes so that every lane gets a share
     const bool dense_pool = d->host_slot_stride == slot_bytes;
+    const int64_t max_run = std::max<int64_t>(1, kStagedMaxCopyBytes / slot_bytes);
+    int copy_no = 0;
     for (int64_t i = 0; i < n;) {
       int64_t j = i + 1;
       if (dense_pool)
-        while (j < n && slot_at(i0 + j) == slot_at(i0 + j - 1) + 1) ++j;
+        while (j < n && j - i < max_run && slot_at(i0 + j) == slot_at(i0 + j - 1) + 1) ++j;
       unsigned char *h = pool + slot_at(i0 + i) * d->host_slot_stride;
       unsigned char *s = stg + i * slot_bytes;
       const size_t nb = (size_t)(j - i) * (size_t)slot_bytes;
-      e = to_host ? cudaMemcpyAsync(h, s, nb, cudaMemcpyDeviceToHost, stream)
-                  : cudaMemcpyAsync(s, h, nb, cudaMemcpyHostToDevice, stream);
+      cudaStream_t cs = lanes ? lanes->lane[copy_no % n_lanes] : stream;
+      e = to_host ? cudaMemcpyAsync(h, s, nb, cudaMemcpyDeviceToHost, cs)
+                  : cudaMemcpyAsync(s, h, nb, cudaMemcpyHostToDevice, cs);
       if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(slot)");
+      ++copy_no;
       i = j;
+    }
+    // join: `stream` continues after every lane has finished its copies
+    if (lanes) {
+      for (int q = 0; q < n_lanes; ++q) {
+        if ((e = cudaEventRecord(lanes->join[q], lanes->lane[q])) != cudaSuccess)
+          return cuda_fail(e, "cudaEventRecord(join)");
+        if ((e = cudaStreamWaitEvent(stream, lanes->join[q], 0)) != cudaSuccess)
+          return cuda_fail(e, "cudaStreamWaitEvent(join)");
+      }
     }
     if (!to_host && (e = pack(false)) != cudaSuccess) return cuda_fail(e, "staging unpack kernel");
   }
@@ -443,6 +538,56 @@ static int relayout_impl(const hfk_relayout_desc *d, int to_host, int ctas, cuda
   return HFK_OK;
 }
 
+// ---- block migration between two caches ----------------------------------------
+static int validate_migrate(const hfk_migrate_desc *d, const char *op) {
+  if (!d) return fail(HFK_ERR_INVALID_ARG, "%s: descriptor is null", op);
+  if (!d->src_k_layer_ptrs || !d->src_v_layer_ptrs || !d->dst_k_layer_ptrs || !d->dst_v_layer_ptrs)
+    return fail(HFK_ERR_INVALID_ARG, "%s: null pointer table", op);
+  if (d->n_blocks < 0 || d->layers <= 0 || d->block_bytes <= 0 || d->num_src_blocks <= 0 || d->num_dst_blocks <= 0)
+    return fail(HFK_ERR_INVALID_ARG, "%s: non-positive geometry", op);
+  if (d->n_blocks > 0 && (!d->src_block_ids || !d->dst_block_ids))
+    return fail(HFK_ERR_INVALID_ARG, "%s: null id list", op);
+  if (d->src_block_stride < d->block_bytes || d->dst_block_stride < d->block_bytes)
+    return fail(HFK_ERR_INVALID_ARG, "%s: block stride smaller than block_bytes", op);
+  if ((d->block_bytes | d->src_block_stride | d->dst_block_stride) & 15)
+    return fail(HFK_ERR_ALIGNMENT, "%s: block_bytes and strides must be multiples of 16 bytes", op);
+  if (d->layers > 2048) return fail(HFK_ERR_TOO_LARGE, "%s: more than 2048 layers", op);
+  return HFK_OK;
+}
+
+static int migrate_impl(const hfk_migrate_desc *d, int ctas, cudaStream_t stream) {
+  int rc = validate_migrate(d, "migrate_blocks");
+  if (rc != HFK_OK) return rc;
+  if (d->n_blocks == 0) return HFK_OK;
+  MigrateArgs a;
+  a.src_k_layer_ptrs = d->src_k_layer_ptrs;
+  a.src_v_layer_ptrs = d->src_v_layer_ptrs;
+  a.dst_k_layer_ptrs = d->dst_k_layer_ptrs;
+  a.dst_v_layer_ptrs = d->dst_v_layer_ptrs;
+  a.src_block_ids = d->src_block_ids;
+  a.dst_block_ids = d->dst_block_ids;
+  a.ids_are_int64 = d->ids_are_int64;
+  a.layers = d->layers;
+  a.n_blocks = d->n_blocks;
+  a.block_bytes = d->block_bytes;
+  a.src_block_stride = d->src_block_stride;
+  a.dst_block_stride = d->dst_block_stride;
+  a.num_src_blocks = d->num_src_blocks;
+  a.num_dst_blocks = d->num_dst_blocks;
+  const int tile = swap_id_tile(d->n_blocks);
+  const size_t smem = migrate_tables_bytes(tile, d->layers);
+  const int64_t items = d->n_blocks * 2 * d->layers;
+  if (ctas <= 0) ctas = sm_count() * kMigrateCtasPerSm;
+  if (ctas > items) ctas = (int)items;
+  auto k = kv_migrate_vector_kernel<512, 4>;
+  cudaError_t e = allow_smem(k, smem);
+  if (e != cudaSuccess) return cuda_fail(e, "kv_migrate_vector_kernel attribute");
+  k<<<ctas, 512, smem, stream>>>(a, tile);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "kv_migrate_vector_kernel launch");
+  return HFK_OK;
+}
+
 // ---- Group R ---------------------------------------------------------------
 static int row_gather_impl(const void *table, void *dst, const void *ids, int ids64, size_t num_ids,
                            size_t row_bytes, size_t num_rows, int ctas, cudaStream_t stream) {
@@ -476,8 +621,9 @@ static int row_gather_impl(const void *table, void *dst, const void *ids, int id
   return HFK_OK;
 }
 
-static int transfer_impl(void *const *layer_ptrs, const void *src, int64_t B, int64_t L, int64_t H,
-                         int64_t D, int64_t elt, int ctas, cudaStream_t stream) {
+// Every argument check of the block transfer; nothing is enqueued before it passes.
+static int validate_transfer(void *const *layer_ptrs, const void *src, int64_t B, int64_t L, int64_t H,
+                             int64_t D, int64_t elt) {
   if (!layer_ptrs || !src)
     return fail(HFK_ERR_INVALID_ARG, "multi_layer_block_transfer: null pointer table or source block");
   if (B <= 0 || L <= 0 || H <= 0 || D <= 0 || elt <= 0)
@@ -488,6 +634,13 @@ static int transfer_impl(void *const *layer_ptrs, const void *src, int64_t B, in
                 (long long)(D * elt));
   if (!aligned16(src)) return fail(HFK_ERR_ALIGNMENT, "multi_layer_block_transfer: source is not 16-byte aligned");
   if (L > 4096) return fail(HFK_ERR_TOO_LARGE, "multi_layer_block_transfer: more than 4096 layers");
+  return HFK_OK;
+}
+
+static int transfer_impl(void *const *layer_ptrs, const void *src, int64_t B, int64_t L, int64_t H,
+                         int64_t D, int64_t elt, int ctas, cudaStream_t stream) {
+  const int rc = validate_transfer(layer_ptrs, src, B, L, H, D, elt);
+  if (rc != HFK_OK) return rc;
   TransferArgs a;
   a.layer_ptrs = layer_ptrs;
   a.src = static_cast<const unsigned char *>(src);
@@ -530,16 +683,18 @@ const char *hfk_version(void) { return "0.1.0"; }
 
 int hfk_device_status(unsigned int *status_bits, hfk_stream_t stream) {
   if (!status_bits) return fail(HFK_ERR_INVALID_ARG, "device_status: null output");
-  cudaError_t e = cudaStreamSynchronize(stream);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+  // read and clear in ONE atomic exchange on the device, so a bit raised by a kernel on another
+  // stream is either in this snapshot or stays for the next read, never lost in between
+  const unsigned int slot = g_status_ticket.fetch_add(1) % kStatusSnapshots;
+  status_exchange_kernel<<<1, 1, 0, stream>>>(slot);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "status_exchange_kernel launch");
   unsigned int v = 0;
-  e = cudaMemcpyFromSymbol(&v, g_status_word, sizeof(v));
-  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyFromSymbol(status)");
-  if (v != 0) {
-    const unsigned int zero = 0;
-    e = cudaMemcpyToSymbol(g_status_word, &zero, sizeof(zero));
-    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyToSymbol(status)");
-  }
+  e = cudaMemcpyFromSymbolAsync(&v, g_status_snapshot, sizeof(v), slot * sizeof(unsigned int),
+                                cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyFromSymbolAsync(status)");
+  e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
   *status_bits = v;
   return HFK_OK;
 }
@@ -580,6 +735,13 @@ int hfk_set_bulk_geometry(int stage_bytes, int n_stages) {
 }
 
 int hfk_set_vector_geometry(int threads, int unroll) {
+  const bool compiled = (threads == 0 && unroll == 0) || (threads == 512 && unroll == 4) ||
+                        (threads == 256 && unroll == 8) || (threads == 256 && unroll == 4) ||
+                        (threads == 1024 && unroll == 2) || (threads == 128 && unroll == 8);
+  if (!compiled)
+    return fail(HFK_ERR_UNSUPPORTED,
+                "vector geometry %dx%d is not compiled (512x4, 256x8, 256x4, 1024x2, 128x8; 0x0 = default)",
+                threads, unroll);
   g_vec_threads = threads;
   g_vec_unroll = unroll;
   return HFK_OK;
@@ -666,12 +828,108 @@ int hfk_fused_memcpy_multi_layer_block_transfer(void *const *device_layer_ptrs,
   if (block_size <= 0 || layers <= 0 || heads <= 0 || head_dim <= 0 || elt_size <= 0)
     return fail(HFK_ERR_INVALID_ARG, "fused_memcpy_multi_layer_block_transfer: non-positive geometry");
   const size_t bytes = (size_t)block_size * layers * heads * head_dim * elt_size;
+  // all checks first: an error return leaves nothing in the stream and the staging bytes untouched
+  const int rc = validate_transfer(device_layer_ptrs, staging, block_size, layers, heads, head_dim, elt_size);
+  if (rc != HFK_OK) return rc;
   // stage 1 on the copy engine (multi_layer_block_transfer_torch.cpp:97-100) ...
   cudaError_t e = cudaMemcpyAsync(staging, host_block, bytes, cudaMemcpyHostToDevice, stream);
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(staging)");
   // ... stage 2: the same kernel, reading the staging buffer (:105)
   return transfer_impl(device_layer_ptrs, staging, block_size, layers, heads, head_dim, elt_size,
                        ctas, stream);
+}
+
+int hfk_migrate_blocks(const hfk_migrate_desc *desc, int ctas, hfk_stream_t stream) {
+  return migrate_impl(desc, ctas, stream);
+}
+
+int hfk_migrate_blocks_copy_engine(const hfk_migrate_desc *d, int src_device, int dst_device,
+                                   hfk_stream_t stream) {
+  int rc = validate_migrate(d, "migrate_blocks_copy_engine");
+  if (rc != HFK_OK) return rc;
+  auto id_at = [&](const void *ids, int64_t i) -> int64_t {
+    return d->ids_are_int64 ? static_cast<const int64_t *>(ids)[i] : (int64_t) static_cast<const int32_t *>(ids)[i];
+  };
+  // every array of the descriptor is a HOST array here; the ids are checked before anything is enqueued
+  for (int64_t i = 0; i < d->n_blocks; ++i) {
+    const int64_t s = id_at(d->src_block_ids, i), t = id_at(d->dst_block_ids, i);
+    if (s < 0 || s >= d->num_src_blocks || t < 0 || t >= d->num_dst_blocks)
+      return fail(HFK_ERR_INVALID_ARG, "migrate_blocks_copy_engine: block id pair (%lld, %lld) out of range at %lld",
+                  (long long)s, (long long)t, (long long)i);
+  }
+  for (int l = 0; l < d->layers; ++l)
+    if (!layer_ptr_ok(d->src_k_layer_ptrs[l]) || !layer_ptr_ok(d->src_v_layer_ptrs[l]) ||
+        !layer_ptr_ok(d->dst_k_layer_ptrs[l]) || !layer_ptr_ok(d->dst_v_layer_ptrs[l]))
+      return fail(HFK_ERR_ALIGNMENT, "migrate_blocks_copy_engine: layer %d has a null or misaligned base", l);
+  for (int64_t i = 0; i < d->n_blocks; ++i) {
+    const int64_t s = id_at(d->src_block_ids, i), t = id_at(d->dst_block_ids, i);
+    for (int l = 0; l < d->layers; ++l)
+      for (int kv = 0; kv < 2; ++kv) {
+        const unsigned char *sp = static_cast<const unsigned char *>(kv ? d->src_v_layer_ptrs[l] : d->src_k_layer_ptrs[l]) +
+                                  s * d->src_block_stride;
+        unsigned char *dp = static_cast<unsigned char *>(kv ? d->dst_v_layer_ptrs[l] : d->dst_k_layer_ptrs[l]) +
+                            t * d->dst_block_stride;
+        cudaError_t e = src_device == dst_device
+                            ? cudaMemcpyAsync(dp, sp, (size_t)d->block_bytes, cudaMemcpyDeviceToDevice, stream)
+                            : cudaMemcpyPeerAsync(dp, dst_device, sp, src_device, (size_t)d->block_bytes, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyPeerAsync(chunk)");
+      }
+  }
+  return HFK_OK;
+}
+
+int hfk_enable_peer_access(int peer_device) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (peer_device == dev) return HFK_OK;
+  int can = 0;
+  e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceCanAccessPeer");
+  if (!can) return fail(HFK_ERR_UNSUPPORTED, "device %d cannot access device %d as a peer", dev, peer_device);
+  e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();
+    return HFK_OK;
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceEnablePeerAccess");
+  return HFK_OK;
+}
+
+int hfk_set_staged_copy_lanes(int lanes) {
+  if (lanes < 0 || lanes > kMaxLanes)
+    return fail(HFK_ERR_INVALID_ARG, "staged copy lanes: 0 (default) .. %d", kMaxLanes);
+  g_staged_lanes = lanes;
+  return HFK_OK;
+}
+
+// ---- diagnostics: per-CTA time stamps ----------------------------------------------
+__global__ void stamp_marker_kernel() {
+  CtaStamp st;
+  st.begin(kStampMarker);
+  st.end();
+}
+
+int hfk_debug_set_stamps(void *device_buffer, size_t buffer_bytes) {
+  unsigned long long *buf = static_cast<unsigned long long *>(device_buffer);
+  unsigned int cap = 0;
+  if (buf != nullptr) {
+    if (buffer_bytes < 8 + 32 || (reinterpret_cast<uintptr_t>(buf) & 7))
+      return fail(HFK_ERR_INVALID_ARG, "debug stamps: buffer must be 8-byte aligned and hold at least one record");
+    cap = (unsigned int)std::min<size_t>((buffer_bytes - 8) / 32, 1u << 30);
+  }
+  cudaError_t e = cudaMemcpyToSymbol(g_stamp_cap, &cap, sizeof(cap));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyToSymbol(stamp capacity)");
+  e = cudaMemcpyToSymbol(g_stamp_buf, &buf, sizeof(buf));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyToSymbol(stamp buffer)");
+  return HFK_OK;
+}
+
+int hfk_debug_stamp_marker(hfk_stream_t stream) {
+  stamp_marker_kernel<<<1, 1, 0, stream>>>();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "stamp_marker_kernel launch");
+  return HFK_OK;
 }
 
 // ---- staged transfer for callers that cannot allocate -------------------------
@@ -742,6 +1000,9 @@ int hfk_fused_memcpy_multi_layer_block_transfer_static(void *const *device_layer
   }
   void *staging = nullptr;
   int rc = static_staging_for_current_device(&staging);
+  if (rc != HFK_OK) return rc;
+  // all checks first: an error return leaves nothing in the stream and the shared block untouched
+  rc = validate_transfer(device_layer_ptrs, staging, block_size, layers, heads, head_dim, elt_size);
   if (rc != HFK_OK) return rc;
   // Nothing in the staging block has to start at zero: the first `bytes` bytes are
   // overwritten by this copy before the kernel reads exactly those bytes.

@@ -35,5 +35,11 @@ constexpr int kGatherVectorCtasPerSm = 2;  // vector mover: 256 threads x 8 load
 constexpr int kDefaultRowGatherCtas = 32;
 constexpr int kDefaultTransferCtas = 32;
 constexpr int kDefaultRelayoutCtas = 32;
+// Staged swap: copy-engine lanes the slot copies are dealt to, and the largest single copy (a run of
+// consecutive slots is cut at this size so that every lane gets work).
+constexpr int kDefaultStagedLanes = 2;
+constexpr long long kStagedMaxCopyBytes = 64ll << 20;
+// Block migration: 512-thread CTAs per SM (peer loads over NVLink need megabytes in flight).
+constexpr int kMigrateCtasPerSm = 2;
 
 }  // namespace hfk

@@ -59,10 +59,18 @@ __device__ __forceinline__ SwapTables carve_swap_tables(unsigned char *base, int
   return t;
 }
 
+// Copies the two pointer tables into shared memory.  An entry that is null or not 16-byte
+// aligned is stored as null and reported; the copy loops skip every chunk of such a layer, so
+// a bad table entry never becomes an address.
+__device__ __forceinline__ unsigned char *checked_layer_ptr(void *p) {
+  if (layer_ptr_ok(p)) return static_cast<unsigned char *>(p);
+  raise_status(HFK_DEV_BAD_LAYER_PTR);
+  return nullptr;
+}
 __device__ __forceinline__ void stage_layer_ptrs(const SwapArgs &a, unsigned char **lp) {
   for (int l = threadIdx.x; l < a.layers; l += blockDim.x) {
-    lp[l] = static_cast<unsigned char *>(a.k_layer_ptrs[l]);
-    lp[a.layers + l] = static_cast<unsigned char *>(a.v_layer_ptrs[l]);
+    lp[l] = checked_layer_ptr(a.k_layer_ptrs[l]);
+    lp[a.layers + l] = checked_layer_ptr(a.v_layer_ptrs[l]);
   }
 }
 
@@ -91,6 +99,8 @@ __global__ void __launch_bounds__(kThreads) kv_swap_vector_kernel(SwapArgs a, in
   const SwapTables tables = carve_swap_tables(smem_raw, id_tile);
   const SwapTables *t = &tables;
   unsigned char **lp = tables.layer_ptrs;
+  CtaStamp stamp;
+  stamp.begin(kStampSwapVector);
   stage_layer_ptrs(a, lp);
   const int per_block = 2 * a.layers;
   const int64_t n16 = a.block_bytes >> 4;
@@ -105,8 +115,9 @@ __global__ void __launch_bounds__(kThreads) kv_swap_vector_kernel(SwapArgs a, in
       const int r = (int)(w - (int64_t)i * per_block);
       const int l = r >> 1, kv = r & 1;
       const int64_t doff = t->dev_off[i];
-      if (doff < 0) continue;
-      unsigned char *d = lp[kv * a.layers + l] + doff;
+      unsigned char *base = lp[kv * a.layers + l];
+      if (doff < 0 || base == nullptr) continue;
+      unsigned char *d = base + doff;
       unsigned char *h =
           a.host_pool + t->host_off[i] + (int64_t)l * a.host_layer_stride + kv * a.host_kv_stride;
       if (kToHost)
@@ -117,6 +128,7 @@ __global__ void __launch_bounds__(kThreads) kv_swap_vector_kernel(SwapArgs a, in
                                       reinterpret_cast<const uint4 *>(h), n16);
     }
   }
+  stamp.end();
 }
 
 // ---- mover 2: one warp per CTA pumping bulk copies -------------------------
@@ -131,6 +143,8 @@ __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_
   const SwapTables tables = carve_swap_tables(reinterpret_cast<unsigned char *>(ps) + sizeof(PumpSmem), id_tile);
   const SwapTables *t = &tables;
   unsigned char **lp = tables.layer_ptrs;
+  CtaStamp stamp;
+  stamp.begin(kStampSwapBulk);
   if (threadIdx.x == 0) {
     for (int s = 0; s < n_stages; ++s) mbar_init(&ps->full[s], 1);
     mbar_fence_init();
@@ -148,7 +162,7 @@ __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_
     const int64_t units = (int64_t)tn * per_block * pieces;
     // this CTA's units are g = blockIdx.x + k*gridDim.x
     const int64_t mine = units > blockIdx.x ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    run_pump<kLag>(ps, stages, stage_bytes, n_stages, mine, seq, [&](int64_t k) {
+    const bool ok = run_pump<kLag>(ps, stages, stage_bytes, n_stages, mine, seq, [&](int64_t k) {
       const int64_t g = blockIdx.x + k * (int64_t)gridDim.x;
       const int64_t w = g / pieces;
       const int piece = (int)(g - w * pieces);
@@ -158,9 +172,10 @@ __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_
       CopyDesc d;
       d.src = nullptr; d.dst = nullptr; d.bytes = 0;
       const int64_t doff = t->dev_off[i];
-      if (doff < 0) return d;
+      unsigned char *base = lp[kv * a.layers + l];
+      if (doff < 0 || base == nullptr) return d;
       const int64_t off = (int64_t)piece * stage_bytes;
-      unsigned char *dp = lp[kv * a.layers + l] + doff + off;
+      unsigned char *dp = base + doff + off;
       unsigned char *hp = a.host_pool + t->host_off[i] + (int64_t)l * a.host_layer_stride +
                           kv * a.host_kv_stride + off;
       d.bytes = (uint32_t)min((int64_t)stage_bytes, a.block_bytes - off);
@@ -168,7 +183,9 @@ __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_
       d.dst = kToHost ? hp : dp;
       return d;
     });
+    if (!ok) break;  // a wait ran out: the barriers are out of step, issue nothing more
   }
+  stamp.end();
 }
 
 }  // namespace hfk

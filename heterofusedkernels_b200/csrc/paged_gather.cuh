@@ -149,8 +149,9 @@ __global__ void __launch_bounds__(kThreads) paged_gather_vector_kernel(GatherArg
     const int l = lk >> 1, kv = lk & 1;
     const PageCopy c = locate_page(a, t, p);
     if (c.bytes == 0) continue;
-    const unsigned char *src =
-        static_cast<const unsigned char *>(kv ? a.v_layer_ptrs[l] : a.k_layer_ptrs[l]) + c.src_off;
+    const unsigned char *base = checked_layer_ptr(kv ? a.v_layer_ptrs[l] : a.k_layer_ptrs[l]);
+    if (base == nullptr) continue;
+    const unsigned char *src = base + c.src_off;
     unsigned char *dst = (kv ? a.v_out : a.k_out) + (int64_t)l * a.out_layer_stride + c.dst_off;
     cta_copy16<kThreads, kUnroll>(reinterpret_cast<uint4 *>(dst),
                                   reinterpret_cast<const uint4 *>(src), c.bytes >> 4);
@@ -196,8 +197,9 @@ __global__ void __launch_bounds__(32) paged_gather_bulk_kernel(GatherArgs a, int
     const PageCopy c = locate_page(a, t, p);
     const int64_t off = (int64_t)piece * stage_bytes;
     if (c.bytes <= off) return d;  // skipped page, or a piece beyond a partial page
-    d.src = static_cast<const unsigned char *>(kv ? a.v_layer_ptrs[l] : a.k_layer_ptrs[l]) +
-            c.src_off + off;
+    const unsigned char *base = checked_layer_ptr(kv ? a.v_layer_ptrs[l] : a.k_layer_ptrs[l]);
+    if (base == nullptr) return d;  // null or misaligned layer base: reported, never dereferenced
+    d.src = base + c.src_off + off;
     d.dst = (kv ? a.v_out : a.k_out) + (int64_t)l * a.out_layer_stride + c.dst_off + off;
     d.bytes = (uint32_t)min((int64_t)stage_bytes, c.bytes - off);
     return d;

@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(kThreads) kv_relayout_swap_kernel(RelayoutArgs
   RelayoutTables *t = reinterpret_cast<RelayoutTables *>(smem_raw);
   unsigned char **lp = reinterpret_cast<unsigned char **>(smem_raw + sizeof(RelayoutTables));
   for (int l = threadIdx.x; l < a.layers; l += kThreads)
-    lp[l] = static_cast<unsigned char *>(a.layer_ptrs[l]);
+    lp[l] = checked_layer_ptr(a.layer_ptrs[l]);  // null when the entry is unusable (reported)
   const int64_t per_block = a.block_size * a.layers * a.heads * a.d16;  // 16-byte vectors per block
   const int64_t stride = (int64_t)gridDim.x * kThreads;
   // one 16-byte vector: v = (block i of the tile, offset r in host order)
@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(kThreads) kv_relayout_swap_kernel(RelayoutArgs
     q /= a.heads;
     const int64_t l = q % a.layers;
     const int64_t tok = q / a.layers;
+    if (lp[l] == nullptr) return false;
     host = reinterpret_cast<const uint4 *>(a.host_pool + t->host_off[i]) + r;
     dev = reinterpret_cast<uint4 *>(lp[l] + doff) + (h * a.block_size + tok) * a.d16 + dv;
     return true;

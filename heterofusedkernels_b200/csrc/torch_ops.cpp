@@ -22,6 +22,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime_api.h>
 #include <torch/library.h>
 
 #include <string>
@@ -240,14 +241,27 @@ void swap_in_staged(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs, 
               deviceBlockStride, aiv, 0, "swap_in_staged");
 }
 
+// Device that owns the memory a raw device address points into (the first entry of a CPU-resident
+// pointer table); falls back to the current device when the driver does not know the address.
+static c10::Device device_of_address(int64_t address) {
+  cudaPointerAttributes attr;
+  if (address != 0 && cudaPointerGetAttributes(&attr, reinterpret_cast<const void *>(address)) == cudaSuccess &&
+      attr.type == cudaMemoryTypeDevice)
+    return c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(attr.device));
+  cudaGetLastError();
+  return c10::Device(c10::kCUDA, c10::cuda::current_device());
+}
+
 // Copy-engine twins: every tensor argument lives on the CPU (the addresses are
-// formed on the host); the copies run on the current stream of the current device.
+// formed on the host); the copies run on the current stream of the device that
+// owns the cache (taken from the first layer pointer).
 void swap_out_copy_engine(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs,
                           const at::Tensor &hostPool, const at::Tensor &deviceBlockIds,
                           const at::Tensor &hostSlotIds, int64_t numDeviceBlocks,
                           c10::optional<int64_t> deviceBlockStride) {
   const hfk_swap_desc d = swap_desc(kLayerPtrs, vLayerPtrs, hostPool, deviceBlockIds, hostSlotIds,
                                     numDeviceBlocks, deviceBlockStride, false, "swap_out_copy_engine");
+  const c10::cuda::CUDAGuard guard(device_of_address(kLayerPtrs.numel() ? kLayerPtrs[0].item<int64_t>() : 0));
   check_rc(hfk_swap_copy_engine(&d, 1, at::cuda::getCurrentCUDAStream().stream()), "swap_out_copy_engine");
 }
 
@@ -257,6 +271,7 @@ void swap_in_copy_engine(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerP
                          c10::optional<int64_t> deviceBlockStride) {
   const hfk_swap_desc d = swap_desc(kLayerPtrs, vLayerPtrs, hostPool, deviceBlockIds, hostSlotIds,
                                     numDeviceBlocks, deviceBlockStride, false, "swap_in_copy_engine");
+  const c10::cuda::CUDAGuard guard(device_of_address(kLayerPtrs.numel() ? kLayerPtrs[0].item<int64_t>() : 0));
   check_rc(hfk_swap_copy_engine(&d, 0, at::cuda::getCurrentCUDAStream().stream()), "swap_in_copy_engine");
 }
 
@@ -359,6 +374,47 @@ void paged_gather(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs, co
            "paged_gather");
 }
 
+// Block migration between two caches.  The four pointer tables and the two id lists are device
+// tensors on the GPU that runs the kernel (the current device of the tables); the addresses in
+// the tables may belong to a peer GPU whose access has been enabled (torch enables it on the
+// first cross-device copy; hfk_enable_peer_access does it explicitly).
+void migrate_blocks(const at::Tensor &srcKLayerPtrs, const at::Tensor &srcVLayerPtrs,
+                    const at::Tensor &dstKLayerPtrs, const at::Tensor &dstVLayerPtrs,
+                    const at::Tensor &srcBlockIds, const at::Tensor &dstBlockIds, int64_t blockBytes,
+                    int64_t numSrcBlocks, int64_t numDstBlocks, c10::optional<int64_t> srcBlockStride,
+                    c10::optional<int64_t> dstBlockStride, c10::optional<int64_t> aiv) {
+  const int ctas = cores_from(aiv);
+  hfk_migrate_desc d;
+  d.layers = static_cast<int>(srcKLayerPtrs.numel());
+  check_ptr_table(srcKLayerPtrs, d.layers, "migrate_blocks(srcKLayerPtrs)", true);
+  check_ptr_table(srcVLayerPtrs, d.layers, "migrate_blocks(srcVLayerPtrs)", true);
+  check_ptr_table(dstKLayerPtrs, d.layers, "migrate_blocks(dstKLayerPtrs)", true);
+  check_ptr_table(dstVLayerPtrs, d.layers, "migrate_blocks(dstVLayerPtrs)", true);
+  d.ids_are_int64 = ids_are_int64(srcBlockIds, "migrate_blocks");
+  TORCH_CHECK(ids_are_int64(dstBlockIds, "migrate_blocks") == d.ids_are_int64,
+              "migrate_blocks: both id lists must have the same dtype");
+  TORCH_CHECK(srcBlockIds.numel() == dstBlockIds.numel(), "migrate_blocks: id lists differ in length");
+  TORCH_CHECK(srcBlockIds.is_cuda() && dstBlockIds.is_cuda(), "migrate_blocks: id lists must be device tensors");
+  const auto dev = srcKLayerPtrs.device();
+  TORCH_CHECK(srcVLayerPtrs.device() == dev && dstKLayerPtrs.device() == dev && dstVLayerPtrs.device() == dev &&
+                  srcBlockIds.device() == dev && dstBlockIds.device() == dev,
+              "migrate_blocks: pointer tables and id lists must live on the GPU that runs the kernel");
+  d.src_k_layer_ptrs = reinterpret_cast<void *const *>(srcKLayerPtrs.data_ptr());
+  d.src_v_layer_ptrs = reinterpret_cast<void *const *>(srcVLayerPtrs.data_ptr());
+  d.dst_k_layer_ptrs = reinterpret_cast<void *const *>(dstKLayerPtrs.data_ptr());
+  d.dst_v_layer_ptrs = reinterpret_cast<void *const *>(dstVLayerPtrs.data_ptr());
+  d.src_block_ids = srcBlockIds.data_ptr();
+  d.dst_block_ids = dstBlockIds.data_ptr();
+  d.n_blocks = srcBlockIds.numel();
+  d.block_bytes = blockBytes;
+  d.src_block_stride = srcBlockStride.has_value() ? srcBlockStride.value() : blockBytes;
+  d.dst_block_stride = dstBlockStride.has_value() ? dstBlockStride.value() : blockBytes;
+  d.num_src_blocks = numSrcBlocks;
+  d.num_dst_blocks = numDstBlocks;
+  const c10::cuda::CUDAGuard guard(dev);
+  check_rc(hfk_migrate_blocks(&d, ctas, at::cuda::getCurrentCUDAStream().stream()), "migrate_blocks");
+}
+
 // Reads and clears the device status word of the current device (bits HFK_DEV_*).
 int64_t device_status() {
   unsigned int bits = 0;
@@ -385,6 +441,7 @@ TORCH_LIBRARY_FRAGMENT(pcie_through, m) {
   m.def("swap_in_staged(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, Tensor staging, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None) -> ()");
   m.def("swap_in_relayout(Tensor layerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None) -> ()");
   m.def("swap_out_relayout(Tensor layerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None) -> ()");
+  m.def("migrate_blocks(Tensor srcKLayerPtrs, Tensor srcVLayerPtrs, Tensor dstKLayerPtrs, Tensor dstVLayerPtrs, Tensor srcBlockIds, Tensor dstBlockIds, int blockBytes, int numSrcBlocks, int numDstBlocks, int? srcBlockStride=None, int? dstBlockStride=None, int? aiv=None) -> ()");
   m.def("device_status() -> int");
 }
 
@@ -399,6 +456,7 @@ TORCH_LIBRARY_IMPL(pcie_through, CUDA, m) {
   m.impl("swap_in_staged", TORCH_FN(pciethrough::swap_in_staged));
   m.impl("swap_in_relayout", TORCH_FN(pciethrough::swap_in_relayout));
   m.impl("swap_out_relayout", TORCH_FN(pciethrough::swap_out_relayout));
+  m.impl("migrate_blocks", TORCH_FN(pciethrough::migrate_blocks));
 }
 
 // all-CPU argument lists dispatch here; there is no CPU implementation of any

@@ -81,14 +81,23 @@ def spread_device_index(local_rank: int, world: int, visible: int) -> int:
 def rank_id_sets(rank: int, n_sets: int, n_swap: int, num_blocks: int, host_slots: int,
                  seed: int = 1234) -> List[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]:
     """Per-rank seeded id lists for `n_sets` steps: (device ids to swap out, host slots, device ids to
-    swap in).  Within a set each list holds distinct ids; different ranks get different lists."""
+    swap in).  Within a set each list holds distinct ids and the swap-in ids differ from the swap-out
+    ids (the blocks come back to *other* device blocks); the slots of consecutive sets are disjoint, so a
+    step may read the previous step's slots while it writes its own.  Different ranks get different
+    lists.  Needs num_blocks >= 2*n_swap and host_slots >= 2*n_swap."""
+    assert num_blocks >= 2 * n_swap and host_slots >= 2 * n_swap, "pools too small for disjoint id sets"
     gen = torch.Generator().manual_seed(seed + rank)
     sets = []
+    prev_slots = torch.empty(0, dtype=torch.int64)
     for _ in range(n_sets):
-        out_ids = torch.randperm(num_blocks, generator=gen)[:n_swap]
-        slots = torch.randperm(host_slots, generator=gen)[:n_swap]
-        in_ids = torch.randperm(num_blocks, generator=gen)[:n_swap]
-        sets.append((out_ids, slots, in_ids))
+        blocks = torch.randperm(num_blocks, generator=gen)
+        out_ids, in_ids = blocks[:n_swap], blocks[n_swap:2 * n_swap]
+        cand = torch.randperm(host_slots, generator=gen)[:2 * n_swap]
+        if prev_slots.numel():
+            cand = cand[~torch.isin(cand, prev_slots)]
+        slots = cand[:n_swap]
+        prev_slots = slots
+        sets.append((out_ids.clone(), slots.clone(), in_ids.clone()))
     return sets
 
 

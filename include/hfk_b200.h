@@ -55,15 +55,21 @@ typedef struct CUstream_st *hfk_stream_t;
 #define HFK_DEV_BAD_HOST_SLOT_ID 0x2u    /* host slot id outside [0, num_host_slots) */
 #define HFK_DEV_BAD_ROW_ID 0x4u          /* gather row id outside [0, num_rows) */
 #define HFK_DEV_BAD_SEQ_LEN 0x8u         /* sequence longer than its block table row */
-#define HFK_DEV_WAIT_TIMEOUT 0x10u       /* a bounded mbarrier wait gave up */
+#define HFK_DEV_WAIT_TIMEOUT 0x10u       /* a bounded mbarrier wait gave up; the destination of that call is undefined */
+#define HFK_DEV_BAD_LAYER_PTR 0x20u      /* a layer base in a device pointer table is null or not 16-byte aligned */
 
 const char *hfk_strerror(int code);
 const char *hfk_last_error_message(void);
 /* Library version, "major.minor.patch". */
 const char *hfk_version(void);
 
-/* Reads the status word of the current device into *status_bits and clears it.
- * Synchronises `stream` first, so it is not for the hot loop. */
+/* Reads the status word of the current device into *status_bits and clears it, in one atomic
+ * exchange executed on `stream` (so it sees every kernel enqueued on `stream` before it), then
+ * synchronises `stream`: not for the hot loop.
+ * The word is per DEVICE, not per stream or per caller: every kernel of this library on that GPU
+ * ORs into the same word, and a read clears it for everybody.  A caller that runs kernels on
+ * several streams must quiesce them (or make `stream` wait on them) before reading, and two
+ * independent users of one GPU see each other's bits. */
 int hfk_device_status(unsigned int *status_bits, hfk_stream_t stream);
 
 /* Self-test of the kernels' bounded waits: a one-warp kernel waits on a barrier that nothing
@@ -84,6 +90,19 @@ int hfk_set_vector_geometry(int threads, int unroll);
  * blocked = 1 gives every CTA one contiguous run of pages instead of every grid-th page.
  * -1 restores the default of either. */
 int hfk_set_gather_tuning(int l2_hints, int blocked);
+/* Staged swap: how many internal copy streams ("lanes") the per-slot copies are dealt to
+ * (1 = all on the caller's stream; up to 4; 0 restores the default). */
+int hfk_set_staged_copy_lanes(int lanes);
+
+/* Diagnostics: per-CTA time stamps.  With a device buffer installed, thread 0 of every CTA of
+ * the swap / migrate kernels appends {tag << 32 | SM id, CTA index, start ns, end ns}
+ * (4 x uint64, %globaltimer) after the record counter in word 0; records beyond the capacity
+ * are counted but not written.  hfk_debug_stamp_marker enqueues a one-thread kernel that
+ * appends a record with tag 0, to mark a point of a stream on the same clock.  Passing NULL
+ * removes the buffer.  The setting is per device (the current one) and is meant for
+ * measurements, not for production: the caller zeroes and reads the buffer. */
+int hfk_debug_set_stamps(void *device_buffer, size_t buffer_bytes);
+int hfk_debug_stamp_marker(hfk_stream_t stream);
 
 /* ======================================================================== *
  *  Host-memory registry and NUMA-local pinned allocation
@@ -312,6 +331,46 @@ typedef struct hfk_relayout_desc {
  * (pcieThrough/csrc/kernel/multi_layer_block_transfer_kernel.h:42-82) to id lists and to the
  * device->host direction. */
 int hfk_swap_relayout(const hfk_relayout_desc *desc, int to_host, int ctas, hfk_stream_t stream);
+
+/* ---- block migration between two caches (one GPU, or two GPUs over NVLink) ----------------
+ * No counterpart function in the reference, whose transfers are host<->device only; it is the
+ * step next to the swap path: moving KV blocks between the caches of two GPUs (or inside one)
+ * without a detour through the host. */
+typedef struct hfk_migrate_desc {
+  /* DEVICE arrays (in the memory of the GPU that runs the kernel) of `layers` cache bases.
+   * The source bases, the destination bases, or neither may point into a peer GPU's memory
+   * (peer access enabled, see hfk_enable_peer_access). */
+  void *const *src_k_layer_ptrs;
+  void *const *src_v_layer_ptrs;
+  void *const *dst_k_layer_ptrs;
+  void *const *dst_v_layer_ptrs;
+  /* DEVICE arrays of n_blocks ids (int64 when ids_are_int64 != 0, else int32). */
+  const void *src_block_ids;
+  const void *dst_block_ids;
+  int ids_are_int64;
+  int layers;
+  int64_t n_blocks;
+  int64_t block_bytes;       /* multiple of 16 */
+  int64_t src_block_stride;  /* >= block_bytes */
+  int64_t dst_block_stride;
+  int64_t num_src_blocks;    /* range checks */
+  int64_t num_dst_blocks;
+} hfk_migrate_desc;
+
+/* For every i < n_blocks, layer l, kv: dst chunk(dst_block_ids[i], l, kv) = src chunk(src_block_ids[i], l, kv),
+ * one launch on the current device.  Launched on the destination GPU it pulls (peer loads,
+ * local stores); launched on the source GPU it pushes.  Only 16-byte vector loads and stores
+ * touch peer memory.  Destination ids must be distinct. */
+int hfk_migrate_blocks(const hfk_migrate_desc *desc, int ctas, hfk_stream_t stream);
+
+/* Copy-engine alternative: one cudaMemcpyPeerAsync (cudaMemcpyAsync when src_device ==
+ * dst_device) per chunk.  All arrays of the descriptor are HOST arrays here. */
+int hfk_migrate_blocks_copy_engine(const hfk_migrate_desc *desc_with_host_arrays, int src_device,
+                                   int dst_device, hfk_stream_t stream);
+
+/* Lets the current device address `peer_device`'s memory (cudaDeviceEnablePeerAccess; already
+ * enabled is not an error). */
+int hfk_enable_peer_access(int peer_device);
 
 typedef struct hfk_paged_gather_desc {
   void *const *k_layer_ptrs; /* DEVICE arrays of `layers` cache bases, as in hfk_swap_desc */

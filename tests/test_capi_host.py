@@ -37,7 +37,8 @@ def test_error_codes_and_defines_match_header(hfk):
 
 
 def test_struct_layouts_follow_the_header_order(hfk):
-    for struct, cname in ((hfk.SwapDesc, "hfk_swap_desc"), (hfk.PagedGatherDesc, "hfk_paged_gather_desc")):
+    for struct, cname in ((hfk.SwapDesc, "hfk_swap_desc"), (hfk.PagedGatherDesc, "hfk_paged_gather_desc"),
+                          (hfk.RelayoutDesc, "hfk_relayout_desc"), (hfk.MigrateDesc, "hfk_migrate_desc")):
         m = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), HEADER, flags=re.S)
         body = re.sub(r"/\*.*?\*/", "", m.group(1), flags=re.S)
         fields = [re.split(r"[\s\*]+", f.strip())[-1] for f in body.split(";") if f.strip()]
@@ -63,7 +64,10 @@ def _swap_desc(hfk, **over):
     (dict(n_blocks=-1), "HFK_ERR_INVALID_ARG"), (dict(block_bytes=4008), "HFK_ERR_ALIGNMENT"),
     (dict(host_kv_stride=4104), "HFK_ERR_ALIGNMENT"), (dict(host_pool=0x10008), "HFK_ERR_ALIGNMENT"),
     (dict(device_block_stride=2048), "HFK_ERR_INVALID_ARG"), (dict(num_host_slots=0), "HFK_ERR_INVALID_ARG"),
-    (dict(device_block_ids=0), "HFK_ERR_INVALID_ARG"), (dict(layers=5000), "HFK_ERR_TOO_LARGE")])
+    (dict(device_block_ids=0), "HFK_ERR_INVALID_ARG"), (dict(layers=5000), "HFK_ERR_TOO_LARGE"),
+    # strides that let chunks overlap: K on top of V, slots inside a slot, an expanded (stride-0) dimension
+    (dict(host_kv_stride=2048), "HFK_ERR_INVALID_ARG"), (dict(host_slot_stride=8192), "HFK_ERR_INVALID_ARG"),
+    (dict(host_layer_stride=0), "HFK_ERR_INVALID_ARG"), (dict(host_slot_stride=-16384), "HFK_ERR_INVALID_ARG")])
 def test_swap_validation_errors(hfk, over, code):
     d, _keep = _swap_desc(hfk, **over)
     for fn in (hfk.lib().hfk_swap_out, hfk.lib().hfk_swap_in):
@@ -94,7 +98,9 @@ def test_staged_and_relayout_validation_errors(hfk):
     assert lib.hfk_swap_staged(C.byref(d), None, 0x10000, stg, 1 << 20, 1, 0, None) == hfk.HFK_ERR_INVALID_ARG
     buf[:4] = torch.tensor([0, 1, 8, 2])                     # slot 8 of 8: rejected on the host
     assert lib.hfk_swap_staged(C.byref(d), buf.data_ptr(), 0x10000, stg, 1 << 20, 0, 0, None) == hfk.HFK_ERR_INVALID_ARG
-    d2, buf2 = _swap_desc(hfk, host_layer_stride=16384, host_slot_stride=8192)   # layer-major pool
+    d3, buf3 = _swap_desc(hfk, host_slot_stride=16384 - 16)                      # slot stride below one slot
+    assert lib.hfk_swap_staged(C.byref(d3), buf3.data_ptr(), 0x10000, stg, 1 << 20, 0, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    d2, buf2 = _swap_desc(hfk, host_layer_stride=65536, host_slot_stride=8192)   # layer-major pool
     assert lib.hfk_swap_staged(C.byref(d2), buf2.data_ptr(), 0x10000, stg, 1 << 20, 0, 0, None) == hfk.HFK_ERR_UNSUPPORTED
     r = hfk.RelayoutDesc()
     r.layer_ptrs = r.device_block_ids = r.host_slot_ids = buf.data_ptr()
@@ -112,6 +118,69 @@ def test_staged_and_relayout_validation_errors(hfk):
         setattr(r, field, old)
     assert lib.hfk_swap_relayout(None, 1, 0, None) == hfk.HFK_ERR_INVALID_ARG
     assert lib.hfk_set_bulk_lag(9) == hfk.HFK_ERR_INVALID_ARG and lib.hfk_set_bulk_lag(0) == hfk.HFK_OK
+    assert lib.hfk_set_staged_copy_lanes(5) == hfk.HFK_ERR_INVALID_ARG and lib.hfk_set_staged_copy_lanes(0) == hfk.HFK_OK
+
+
+def test_vector_geometry_accepts_only_compiled_combinations(hfk):
+    lib = hfk.lib()
+    for th, un in ((512, 4), (256, 8), (256, 4), (1024, 2), (128, 8), (0, 0)):
+        assert lib.hfk_set_vector_geometry(th, un) == hfk.HFK_OK
+    for th, un in ((512, 8), (64, 4), (0, 4), (-1, -1)):
+        assert lib.hfk_set_vector_geometry(th, un) == hfk.HFK_ERR_UNSUPPORTED
+        assert "not compiled" in hfk.last_error()
+    # a rejected pair leaves the previous (default) setting in place
+    assert lib.hfk_set_vector_geometry(0, 0) == hfk.HFK_OK
+
+
+def test_block_transfer_checks_everything_before_it_enqueues(hfk):
+    """The staged transfers validate the whole call first: with no CUDA device here, reaching the copy
+    would return HFK_ERR_CUDA, so the codes below prove that the checks come before it."""
+    lib = hfk.lib()
+    buf = torch.zeros(64, dtype=torch.int64)
+    p = buf.data_ptr()
+    fused = lib.hfk_fused_memcpy_multi_layer_block_transfer
+    assert fused(p, p, p, 16, 2, 1, 8, 1, 0, None) == hfk.HFK_ERR_ALIGNMENT        # head_dim*elt = 8
+    assert fused(None, p, p, 16, 2, 1, 16, 1, 0, None) == hfk.HFK_ERR_INVALID_ARG  # null pointer table
+    assert fused(p, p, p, 16, 5000, 1, 16, 1, 0, None) == hfk.HFK_ERR_TOO_LARGE    # > 4096 layers
+    assert fused(p, p, p + 8, 16, 2, 1, 16, 1, 0, None) == hfk.HFK_ERR_ALIGNMENT   # misaligned staging
+
+
+def _migrate_desc(hfk, **over):
+    d = hfk.MigrateDesc()
+    buf = torch.zeros(64, dtype=torch.int64)
+    p = buf.data_ptr()
+    d.src_k_layer_ptrs = d.src_v_layer_ptrs = d.dst_k_layer_ptrs = d.dst_v_layer_ptrs = p
+    d.src_block_ids = d.dst_block_ids = p
+    d.ids_are_int64, d.layers, d.n_blocks = 1, 2, 4
+    d.block_bytes = d.src_block_stride = d.dst_block_stride = 4096
+    d.num_src_blocks = d.num_dst_blocks = 8
+    for k, v in over.items():
+        setattr(d, k, v)
+    return d, buf
+
+
+@pytest.mark.parametrize("over,code", [
+    (dict(dst_v_layer_ptrs=0), "HFK_ERR_INVALID_ARG"), (dict(layers=0), "HFK_ERR_INVALID_ARG"),
+    (dict(n_blocks=-2), "HFK_ERR_INVALID_ARG"), (dict(block_bytes=4008), "HFK_ERR_ALIGNMENT"),
+    (dict(src_block_stride=2048), "HFK_ERR_INVALID_ARG"), (dict(dst_block_stride=4104), "HFK_ERR_ALIGNMENT"),
+    (dict(num_dst_blocks=0), "HFK_ERR_INVALID_ARG"), (dict(src_block_ids=0), "HFK_ERR_INVALID_ARG"),
+    (dict(layers=3000), "HFK_ERR_TOO_LARGE")])
+def test_migrate_validation_errors(hfk, over, code):
+    d, _keep = _migrate_desc(hfk, **over)
+    assert hfk.lib().hfk_migrate_blocks(C.byref(d), 0, None) == getattr(hfk, code)
+    assert hfk.lib().hfk_migrate_blocks_copy_engine(C.byref(d), 0, 0, None) == getattr(hfk, code)
+
+
+def test_migrate_copy_engine_checks_ids_and_layer_bases_on_the_host(hfk):
+    lib = hfk.lib()
+    assert lib.hfk_migrate_blocks(None, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    d, buf = _migrate_desc(hfk)
+    buf[:4] = torch.tensor([0, 1, 8, 2])   # id 8 of 8
+    assert lib.hfk_migrate_blocks_copy_engine(C.byref(d), 0, 0, None) == hfk.HFK_ERR_INVALID_ARG
+    assert "out of range" in hfk.last_error()
+    buf[:4] = torch.tensor([0, 1, 3, 2])   # valid ids, but the same words serve as layer bases: 0 is null
+    assert lib.hfk_migrate_blocks_copy_engine(C.byref(d), 0, 0, None) == hfk.HFK_ERR_ALIGNMENT
+    assert "null or misaligned base" in hfk.last_error()
 
 
 def _gather_desc(hfk, **over):

@@ -456,7 +456,7 @@ def test_staged_swap_matches_oracle(hfk, cuda_device, staging_slots):
         bad[3] = nslots
         assert lib.hfk_swap_staged(C.byref(d), bad.data_ptr(), case.pool.ptr, staging.data_ptr(), staging.numel(),
                                    0, 0, stream_handle()) == hfk.HFK_ERR_INVALID_ARG
-        d.host_kv_stride = 4096 * 16
+        d.host_kv_stride = d.host_slot_stride * nslots    # K and V in two separate arrays: valid, but not slot-contiguous
         assert lib.hfk_swap_staged(C.byref(d), slots.data_ptr(), case.pool.ptr, staging.data_ptr(), staging.numel(),
                                    0, 0, stream_handle()) == hfk.HFK_ERR_UNSUPPORTED
     finally:
