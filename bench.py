@@ -61,6 +61,8 @@ def geometry(name: str):
                              host_slots=1, n_swap=1),
         "embedding_gather": NS(layers=1, num_blocks=1, block_size=1, kv_heads=1, head_dim=512, dtype=torch.float16,
                                host_slots=1, n_swap=1),
+        "migrate": NS(layers=32, num_blocks=4096, block_size=16, kv_heads=8, head_dim=128,
+                      dtype=torch.bfloat16, host_slots=0, n_swap=512),
         "tiny": NS(layers=2, num_blocks=64, block_size=16, kv_heads=8, head_dim=128, dtype=torch.float16,
                    host_slots=128, n_swap=8),
     }
@@ -313,18 +315,26 @@ class SwapBench:
                     (odd ranks: in (prev) first)
     """
 
-    def __init__(self, g, cache, ctx, pkg, n_sets: int, mover, aiv, staging_mb: int, slot_runs: bool = False):
+    def __init__(self, g, cache, ctx, pkg, n_sets: int, mover, aiv, staging_mb: int, slot_runs: int = 0):
         self.g, self.cache, self.ctx, self.pkg = g, cache, ctx, pkg
         self.mover, self.aiv, self.staging_bytes = mover, aiv, staging_mb << 20
         from heterofusedkernels_b200 import ranks
 
         self.sets = ranks.rank_id_sets(ctx.rank, n_sets + 1, g.n_swap, g.num_blocks, cache.host_slots)
         if slot_runs:
-            # the slots of a step form one run of consecutive slots, as a fresh free list hands them
-            # out (HostSlotPool); consecutive steps use different runs
-            n_runs = cache.host_slots // g.n_swap
-            self.sets = [(o_ids, torch.arange(g.n_swap) + (s % n_runs) * g.n_swap, i_ids)
-                         for s, (o_ids, _, i_ids) in enumerate(self.sets)]
+            # the slots of a step form runs of `slot_runs` consecutive slots at seeded random places, as a
+            # free list hands them out (HostSlotPool); consecutive steps use different cells of the grid
+            run = min(int(slot_runs), g.n_swap)
+            cells = cache.host_slots // run
+            need = (g.n_swap + run - 1) // run
+            assert cells >= 2 * need, "host pool too small for disjoint runs"
+            gen = torch.Generator().manual_seed(99 + ctx.rank)
+            new_sets = []
+            for s, (o_ids, _, i_ids) in enumerate(self.sets):
+                pick = torch.randperm(cells // 2, generator=gen)[:need] * 2 + (s % 2)
+                slots = (pick.unsqueeze(1) * run + torch.arange(run).unsqueeze(0)).reshape(-1)[:g.n_swap]
+                new_sets.append((o_ids, slots, i_ids))
+            self.sets = new_sets
         self.dev_sets = [tuple(t.to(cache.device) for t in s) for s in self.sets]
         self.pin_sets = [tuple(t.pin_memory() for t in s) for s in self.sets]
         self.side = [torch.cuda.Stream(cache.device), torch.cuda.Stream(cache.device)]
@@ -672,14 +682,15 @@ class OverlapBench:
 
     MAX_GROUP = 8
 
-    def __init__(self, g, device, pkg, host_raw=None):
+    def __init__(self, g, device, pkg, host_raw=None, pool_layout="slot_major", slot_runs=False):
         from heterofusedkernels_b200.connector import LayerwisePrefetcher, PagedKVCache
 
         self.g, self.device, self.pkg = g, device, pkg
+        self.pool_layout, self.slot_runs = pool_layout, slot_runs
         self.cache = PagedKVCache(g.layers, g.num_blocks, g.block_size, g.kv_heads, g.head_dim, g.dtype, device,
                                   host_slots=g.host_slots if host_raw is None else
                                   min(g.host_slots, host_raw.numel() // (g.layers * 2 * g.block_bytes)),
-                                  host_raw=host_raw)
+                                  host_raw=host_raw, pool_layout=pool_layout)
         fill_random_bytes(self.cache._k_store, 1)
         fill_random_bytes(self.cache._v_store, 2)
         self.pf = LayerwisePrefetcher(self.cache)
@@ -696,6 +707,9 @@ class OverlapBench:
             perm = torch.randperm(g.num_blocks, generator=gen)
             sl = torch.randperm(self.cache.host_slots, generator=gen)
             n = g.n_swap
+            if slot_runs:   # two runs of consecutive slots, as a fresh free list hands them out
+                base = int(torch.randint(0, self.cache.host_slots - 2 * n, (1,), generator=gen))
+                sl = torch.arange(base, base + 2 * n)
             self.ids_cpu.append((perm[:n], sl[:n], perm[n:2 * n], sl[n:2 * n]))
         self.ids = [tuple(t.to(device) for t in x) for x in self.ids_cpu]
         # known random bytes wherever a swap-in will read: the in-slots of layer l, for layer l and the
@@ -727,14 +741,23 @@ class OverlapBench:
         return [range(a, min(a + group, self.L)) for a in range(0, self.L, group)]
 
     def run(self, kind, ctas, group: int = 1, with_gemm: bool = True, directions=("in", "out"), markers=False) -> dict:
-        """One pass over all layers.  kind: None (the prefetcher's shipped defaults), "vector", "bulk",
-        "bulk@<stage bytes>x<stages>" or "copy_engine"."""
+        """One pass over all layers.  kind: None (the prefetcher's shipped defaults), "vector" or
+        "vector@<threads>x<loads in flight>[+pad<KiB of unused shared memory>]", "bulk" or "bulk@<stage bytes>x<stages>[+lag<k>]", "staged"
+        (packing kernel + copy-engine transfers) or "copy_engine" (one copy per chunk)."""
         pkg, pf, cache, L = self.pkg, self.pf, self.cache, self.L
         lib = pkg.capi.lib()
-        mv = None if kind is None else (pkg.capi.MOVER_VECTOR if kind == "vector" else
-                                        (pkg.capi.MOVER_BULK if kind.startswith("bulk") else None))
-        ring = tuple(int(x) for x in kind.split("@")[1].split("x")) if kind and "@" in kind else (0, 0)
-        lib.hfk_set_bulk_geometry(*ring)
+        base_kind = (kind or "").split("@")[0].split("+")[0]
+        mv = {"": None, "vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK, "staged": "staged",
+              "copy_engine": None}[base_kind]
+        geo = tuple(int(x) for x in kind.split("@")[1].split("+")[0].split("x")) if kind and "@" in kind else (0, 0)
+        lag = int(kind.split("+lag")[1]) if kind and "+lag" in kind else 0
+        pad_kib = int(kind.split("+pad")[1]) if kind and "+pad" in kind else 0
+        pkg.capi.check(lib.hfk_set_vector_smem_pad(pad_kib * 1024), "hfk_set_vector_smem_pad")
+        if base_kind == "vector":
+            pkg.capi.check(lib.hfk_set_vector_geometry(*geo), "hfk_set_vector_geometry")
+        else:
+            pkg.capi.check(lib.hfk_set_bulk_geometry(*geo), "hfk_set_bulk_geometry")
+        pkg.capi.check(lib.hfk_set_bulk_lag(lag), "hfk_set_bulk_lag")
         groups = self.groups(group)
         ev_in, ev_out = [], []
         torch.cuda.synchronize()
@@ -744,6 +767,7 @@ class OverlapBench:
             nxt = groups[(gi + 1) % len(groups)]
             in_ids, in_slots, _, _ = self.ids[nxt.start]
             _, _, out_ids, out_slots = self.ids[layers.start]
+            in_slots_cpu, out_slots_cpu = self.ids_cpu[nxt.start][1], self.ids_cpu[layers.start][3]
             if kind == "copy_engine":
                 ci_n, ci_l = self.ids_cpu[nxt.start], self.ids_cpu[layers.start]
                 with torch.cuda.stream(pf.in_stream):
@@ -768,7 +792,7 @@ class OverlapBench:
                         if markers:
                             lib.hfk_debug_stamp_marker(pf.in_stream.cuda_stream)
                         a.record()
-                    pf.prefetch(nxt, in_ids, in_slots, aiv=ctas, mover=mv, after=False)
+                    pf.prefetch(nxt, in_ids, in_slots, aiv=ctas, mover=mv, after=False, host_slot_ids_cpu=in_slots_cpu)
                     with torch.cuda.stream(pf.in_stream):
                         b.record()
                     ev_in.append((a, b, len(nxt)))
@@ -779,7 +803,7 @@ class OverlapBench:
                         if markers:
                             lib.hfk_debug_stamp_marker(pf.out_stream.cuda_stream)
                         a.record()
-                    pf.evict(layers, out_ids, out_slots, aiv=ctas, mover=mv, after=False)
+                    pf.evict(layers, out_ids, out_slots, aiv=ctas, mover=mv, after=False, host_slot_ids_cpu=out_slots_cpu)
                     with torch.cuda.stream(pf.out_stream):
                         b.record()
                     ev_out.append((a, b, len(layers)))
@@ -790,6 +814,9 @@ class OverlapBench:
         pf.quiesce()
         torch.cuda.synchronize()
         lib.hfk_set_bulk_geometry(0, 0)
+        lib.hfk_set_vector_geometry(0, 0)
+        lib.hfk_set_vector_smem_pad(0)
+        lib.hfk_set_bulk_lag(0)
 
         def rate(evs):
             if not evs:
@@ -826,6 +853,7 @@ class OverlapBench:
         med_main = statistics.median(r["main_ms"] for r in runs)
         ver = self.verify(group)
         return {"mover": kind or "default", "ctas_per_direction": ctas or "default", "layers_per_launch": group,
+                "pool_layout": self.pool_layout, "slots": "runs" if self.slot_runs else "random",
                 "gemm_ms_alone": t_a, "gemm_ms_overlapped": med_main,
                 "gemm_slowdown_pct": 100.0 * (med_main / t_a - 1.0),
                 "gemm_tflops_alone": self.L * self.flops / (t_a * 1e-3) / 1e12,
@@ -895,18 +923,30 @@ def bench_overlap(g, device, args, pkg) -> dict:
     sampler = ClockSampler(device.index or 0)
     reps = args.overlap_reps
     variants = []
-    table = [(None, None, 1), (None, None, 2), (None, None, 4), (None, None, 7),
-             ("vector", 8, 1), ("vector", 16, 1), ("vector", 16, 4), ("vector", 32, 4), ("vector", 8, 4),
-             ("bulk", 4, 1), ("bulk", 8, 1), ("bulk", 4, 4), ("bulk@2048x4", 32, 1), ("bulk@2048x4", 32, 4),
-             ("bulk@4096x4", 32, 4), ("copy_engine", 0, 1)]
+    table = [(None, None, 1), (None, None, 2), (None, None, 4), (None, None, 8),
+             ("vector", 16, 8), ("vector+pad96", 16, 4), ("vector+pad96", 16, 8), ("vector+pad96", 8, 8),
+             ("vector+pad160", 32, 8), ("bulk", 16, 8), ("bulk", 8, 8),
+             ("vector@256x8", 32, 4), ("vector@128x8", 64, 4),
+             ("bulk@2048x4", 64, 4), ("bulk@2048x4+lag1", 64, 4), ("bulk@4096x4+lag1", 32, 4)]
+    if args.overlap_quick:
+        table = table[:2]
     for kind, ctas, group in table:
-        variants.append(ob.measure(kind, ctas, group, reps if kind != "copy_engine" else 2))
+        variants.append(ob.measure(kind, ctas, group, reps))
     stamps = []
-    for kind, ctas in (("bulk", 4), ("bulk", 8), ("bulk@2048x4", 32), ("vector", 16)):
+    for kind, ctas in (() if args.overlap_quick else
+                       (("bulk", 4), ("bulk@2048x4", 64), ("bulk@4096x4+lag1", 64), ("vector", 16), ("vector@128x8", 64))):
         for direction in ("in", "out"):
             stamps.append(ob.stamps(kind, ctas, 1, direction))
-    clocks = sampler.stop()
     status = ob.cache.status()
+    del ob
+    torch.cuda.empty_cache()
+    # the same pipeline on a layer-major pool with slots handed out as runs: one copy-engine transfer per
+    # layer and direction (staged), next to the kernel movers on the same layout
+    ob = OverlapBench(g, device, pkg, pool_layout="layer_major", slot_runs=True)
+    for kind, ctas, group in (("staged", None, 1), ("staged", None, 4), ("staged@2048x4", 64, 4), (None, None, 4)):
+        variants.append(ob.measure(kind, ctas, group, reps))
+    clocks = sampler.stop()
+    status |= ob.cache.status()
     ok = [v for v in variants if v["mover"] != "copy_engine" and v["gemm_slowdown_pct"] < 10.0]
     pick = max(ok or variants, key=lambda v: v["swap_in_gbs"] + v["swap_out_gbs"])
     L = g.layers
@@ -979,6 +1019,105 @@ def bench_large_swap_beside_gemm(sb: SwapBench, device, steps: int) -> dict:
             "verified": ver["verified"]}
 
 
+# --------------------------------------------------------------------------- GPU <-> GPU migration leg
+def bench_migrate(g, args, pkg) -> dict:
+    """KV block migration between the caches of two GPUs of one box (one process, two devices):
+    512 blocks x 32 layers x K,V of the Llama-3-8B layout (1.07 GB) from GPU 0's cache into other
+    blocks of GPU 1's cache.  Pull (the destination GPU runs the kernel: peer loads over NVLink),
+    push (the source GPU runs it: peer stores), the copy-engine twin (one cudaMemcpyPeerAsync per
+    chunk, fewer blocks) and a plain 1 GiB peer copy as the NVLink denominator; every result is
+    compared byte for byte with the source blocks."""
+    from heterofusedkernels_b200.connector import PagedKVCache
+
+    assert torch.cuda.device_count() >= 2, "the migration leg needs two GPUs in one process"
+    d0, d1 = torch.device("cuda", 0), torch.device("cuda", 1)
+    lib = pkg.capi.lib()
+    src = PagedKVCache(g.layers, g.num_blocks, g.block_size, g.kv_heads, g.head_dim, g.dtype, d0)
+    dst = PagedKVCache(g.layers, g.num_blocks, g.block_size, g.kv_heads, g.head_dim, g.dtype, d1)
+    for i, t in enumerate((src._k_store, src._v_store, dst._k_store, dst._v_store)):
+        fill_random_bytes(t, 10 + i)
+    gen = torch.Generator().manual_seed(3)
+    nbytes = g.swap_bytes
+    # NVLink denominator: one contiguous peer copy of 1 GiB
+    a0 = torch.empty(1 << 30, dtype=torch.uint8, device=d0)
+    a1 = torch.empty(1 << 30, dtype=torch.uint8, device=d1)
+    peer = 0.0
+    with torch.cuda.device(d1):
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            a1.copy_(a0, non_blocking=True)
+            e1.record()
+            e1.synchronize()
+            peer = max(peer, a0.numel() / (e0.elapsed_time(e1) * 1e-3) / GB)
+    del a0, a1
+
+    def check(s_ids, d_ids) -> bool:
+        ok = True
+        for sk, dk in ((src._k_store, dst._k_store), (src._v_store, dst._v_store)):
+            for l0 in range(0, g.layers, 8):
+                want = sk[l0:l0 + 8].index_select(1, s_ids.to(d0)).to(d1)
+                got = dk[l0:l0 + 8].index_select(1, d_ids.to(d1))
+                ok = ok and torch.equal(want.view(torch.int16), got.view(torch.int16))
+        return ok
+
+    rows = {}
+    for mode, run_dev in (("pull", d1), ("push", d0)):
+        for ctas in (None, 148, 296, 592):
+            best, ok = 0.0, True
+            for rep in range(args.warmup + args.steps):
+                s_ids = torch.randperm(g.num_blocks, generator=gen)[:g.n_swap]
+                d_ids = torch.randperm(g.num_blocks, generator=gen)[:g.n_swap]
+                with torch.cuda.device(run_dev):
+                    torch.cuda.synchronize(d0)
+                    torch.cuda.synchronize(d1)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s_dev, d_dev = s_ids.to(run_dev), d_ids.to(run_dev)
+                    e0.record()
+                    src.migrate_to(dst, s_dev, d_dev, aiv=ctas, run_on="dst" if mode == "pull" else "src")
+                    e1.record()
+                    e1.synchronize()
+                    if rep >= args.warmup:
+                        best = max(best, nbytes / (e0.elapsed_time(e1) * 1e-3) / GB)
+                if rep == args.warmup + args.steps - 1:
+                    ok = check(s_ids, d_ids)
+            rows[f"{mode}_ctas_{ctas or 'default'}"] = {"GBps": best, "verified": ok}
+    # copy-engine twin: one cudaMemcpyPeerAsync per 32 KiB chunk (64 blocks = 4096 copies)
+    n_ce = 64
+    s_ids = torch.randperm(g.num_blocks, generator=gen)[:n_ce]
+    d_ids = torch.randperm(g.num_blocks, generator=gen)[:n_ce]
+    md = pkg.capi.MigrateDesc()
+    md.src_k_layer_ptrs, md.src_v_layer_ptrs = src.k_ptrs_cpu.data_ptr(), src.v_ptrs_cpu.data_ptr()
+    md.dst_k_layer_ptrs, md.dst_v_layer_ptrs = dst.k_ptrs_cpu.data_ptr(), dst.v_ptrs_cpu.data_ptr()
+    md.src_block_ids, md.dst_block_ids = s_ids.data_ptr(), d_ids.data_ptr()
+    md.ids_are_int64, md.layers, md.n_blocks, md.block_bytes = 1, g.layers, n_ce, g.block_bytes
+    md.src_block_stride = md.dst_block_stride = g.block_bytes
+    md.num_src_blocks = md.num_dst_blocks = g.num_blocks
+    with torch.cuda.device(d1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        pkg.capi.check(lib.hfk_migrate_blocks_copy_engine(C.byref(md), 0, 1, torch.cuda.current_stream(d1).cuda_stream),
+                       "hfk_migrate_blocks_copy_engine")
+        e1.record()
+        e1.synchronize()
+        rows["copy_engine_per_chunk"] = {"GBps": n_ce * g.layers * 2 * g.block_bytes / (e0.elapsed_time(e1) * 1e-3) / GB,
+                                         "verified": check(s_ids, d_ids), "copies": n_ce * g.layers * 2}
+    status = src.status() | dst.status()
+    best_key = max((k for k in rows if k.startswith(("pull", "push"))), key=lambda k: rows[k]["GBps"])
+    return {"metric": "kv_migrate_GBps", "value": rows[best_key]["GBps"], "unit": "GB/s", "n_gpus": 2, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": nbytes / rows[best_key]["GBps"] / 1e6, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": "migrate", "layers": g.layers, "blocks": g.n_swap, "bytes": nbytes,
+                       "layout": "Llama-3-8B: bf16 [16, 8, 128] blocks, 4096-block caches on GPU 0 and GPU 1",
+                       "l2": "1.07 GB of distinct blocks per launch (larger than L2)"},
+            "best": best_key, "rows": rows, "verified": all(r["verified"] for r in rows.values()),
+            "roofline": {"bound": "nvlink", "achieved": rows[best_key]["GBps"], "peak": peer, "unit": "GB/s",
+                         "frac": rows[best_key]["GBps"] / peer, "traffic": None,
+                         "peak_source": "live cudaMemcpy of 1 GiB GPU 0 -> GPU 1, best of 5 (pool reference: 770 GB/s "
+                                        "per direction)"},
+            "status_word": status, "gpu_launches": args.steps}
+
+
 # --------------------------------------------------------------------------- main
 def main() -> None:
     ap = argparse.ArgumentParser()
@@ -994,8 +1133,8 @@ def main() -> None:
     ap.add_argument("--variants", default="", help="comma-separated extra variants to time after the main one")
     ap.add_argument("--staging-mb", type=int, default=1024, help="staging buffer of the staged mover (MiB)")
     ap.add_argument("--staged-lanes", type=int, default=0, help="copy streams of the staged mover (0 = library default)")
-    ap.add_argument("--slot-runs", action="store_true",
-                    help="each step's host slots form one run of consecutive slots instead of random slots")
+    ap.add_argument("--slot-runs", type=int, default=0,
+                    help="each step's host slots come as runs of this many consecutive slots (0 = random slots)")
     ap.add_argument("--aiv", type=int, default=0, help="CTAs per swap kernel (0 = library default)")
     ap.add_argument("--gather-aiv", type=int, default=0)
     ap.add_argument("--host-slots", type=int, default=0, help="override the host pool size (slots)")
@@ -1003,9 +1142,11 @@ def main() -> None:
     ap.add_argument("--no-spread", action="store_true", help="use GPU ordinal = LOCAL_RANK even when more GPUs are visible")
     ap.add_argument("--no-gather", action="store_true")
     ap.add_argument("--no-config4", action="store_true", help="skip the short Llama-3-70B TP8 run")
+    ap.add_argument("--no-allocator-leg", action="store_true", help="skip the run with allocator-ordered host slots")
     ap.add_argument("--no-overlap", action="store_true", help="skip the short prefetch-next-to-a-GEMM run")
     ap.add_argument("--overlap-group", type=int, default=0, help="layers per prefetch launch (0 = shipped default)")
     ap.add_argument("--overlap-reps", type=int, default=5)
+    ap.add_argument("--overlap-quick", action="store_true", help="overlap study: the shipped defaults only")
     ap.add_argument("--beside-gemm", action="store_true", help="also time the full swap step next to a GEMM loop")
     ap.add_argument("--gather-only", action="store_true", help="run only the paged-gather leg")
     ap.add_argument("--gather-seqs", type=int, default=64, help="sequences in the gather batch")
@@ -1070,6 +1211,9 @@ def main() -> None:
                           "config": {"workload": "llama3_8b_gather", "num_seqs": args.gather_seqs}, "gather": res}),
               flush=True)
         return
+    if g.name == "migrate":
+        print(json.dumps(bench_migrate(g, args, pkg)), flush=True)
+        return
     if g.name == "block_transfer":
         print(json.dumps(bench_block_transfer(device, args, pkg)), flush=True)
         return
@@ -1103,7 +1247,8 @@ def main() -> None:
 
     n_sets = args.warmup + args.steps
     sb = SwapBench(g, cache, ctx, pkg, n_sets, mover, aiv, args.staging_mb, slot_runs=args.slot_runs)
-    config["host_slots_per_step"] = "one run of consecutive slots" if args.slot_runs else "random distinct slots"
+    config["host_slots_per_step"] = (f"runs of {args.slot_runs} consecutive slots" if args.slot_runs
+                                     else "random distinct slots")
 
     pcie = measure_pcie_peak(host_raw.view(torch.uint8), device) if rank == 0 else None
     barrier()
@@ -1161,6 +1306,18 @@ def main() -> None:
         extra[var] = {"value": r["value"], "ms_per_step": r["ms_per_step"], "verified": r["all_verified"],
                       "swap_out_GBps_per_rank": [round(p[0], 2) for p in per],
                       "swap_in_GBps_per_rank": [round(p[1], 2) for p in per], "plan_rank0": r["plan"]}
+    # ---- the same step with the slots a fresh free list hands out (one run per step), public API ----
+    # PagedKVCache then picks the staged mover by itself: the copy engine crosses the link.
+    alloc_leg = None
+    if world == 1 and not args.slot_runs and not args.no_allocator_leg:
+        sb_runs = SwapBench(g, cache, ctx, pkg, n_sets, None, aiv, args.staging_mb, slot_runs=g.n_swap)
+        r = timed_leg(sb_runs, variant, args.steps, args.warmup, e2e=True)
+        alloc_leg = {"value": r["value"], "unit": "GB/s", "ms_per_step": r["ms_per_step"], "swap_out_GBps": r["out_gbs"],
+                     "swap_in_GBps": r["in_gbs"], "verified": r["all_verified"],
+                     "slots": f"one run of {g.n_swap} consecutive host slots per step (HostSlotPool order)",
+                     "mover": "picked by PagedKVCache.swap_out/swap_in: staged (packing kernel + copy-engine "
+                              "transfers of up to 64 MiB)"}
+        del sb_runs
     beside = None
     if args.beside_gemm and world == 1:
         beside = bench_large_swap_beside_gemm(sb, device, min(args.steps, 5))
@@ -1250,6 +1407,10 @@ def main() -> None:
             "concurrent_note": "cudaMemcpyAsync with every rank copying at once: one direction (8 x 1 GiB) and both "
                                "directions on two streams (4 + 4 x 1 GiB, both directions' bytes over the time "
                                "until both are done); roofline.peak is one link alone"})
+    if alloc_leg is not None:
+        roofline.update({"e2e_allocator_slots_gbs": alloc_leg["value"],
+                         "e2e_allocator_slots_frac": alloc_leg["value"] / pcie_peak,
+                         "e2e_allocator_slots_verified": alloc_leg["verified"]})
     if config4 is not None:
         roofline.update({"config4_value": config4["value"], "config4_ms_per_step": config4["ms_per_step"],
                          "config4_swap_out_GBps_per_gpu": config4["swap_out_GBps_per_gpu_mean"],
@@ -1279,6 +1440,8 @@ def main() -> None:
             "host": {"cpus": os.cpu_count(), "mem_available_GB": round(mem_available_bytes() / 1e9, 1)}}
     if extra:
         line["variants"] = extra
+    if alloc_leg is not None:
+        line["allocator_slots"] = alloc_leg
     if beside is not None:
         line["beside_gemm"] = beside
     if config4 is not None:
@@ -1303,7 +1466,7 @@ def main() -> None:
 # How a step is issued when several ranks share the host (see SwapBench); chosen by measurement.
 MULTI_GPU_VARIANT = "stagger"
 # Layers per launch of the prefetch pipeline in the default line's `overlap` run.
-DEFAULT_PREFETCH_GROUP = 1
+DEFAULT_PREFETCH_GROUP = 4
 VARIANT_TEXT = {
     "sequential": "swap-out then swap-in of the same slots, one stream",
     "stagger": "odd ranks swap-in (the previous step's slots) first, even ranks swap-out first",

@@ -128,6 +128,7 @@ PROTOTYPES = {
     "hfk_set_bulk_geometry": (C.c_int, [C.c_int, C.c_int]),
     "hfk_set_bulk_lag": (C.c_int, [C.c_int]),
     "hfk_set_vector_geometry": (C.c_int, [C.c_int, C.c_int]),
+    "hfk_set_vector_smem_pad": (C.c_int, [C.c_int]),
     "hfk_set_gather_tuning": (C.c_int, [C.c_int, C.c_int]),
     "hfk_set_staged_copy_lanes": (C.c_int, [C.c_int]),
     "hfk_debug_set_stamps": (C.c_int, [C.c_void_p, C.c_size_t]),

@@ -57,6 +57,7 @@ __global__ void status_exchange_kernel(unsigned int slot) {
 std::atomic<int> g_stage_bytes{0}, g_n_stages{0}, g_bulk_lag{0}, g_vec_threads{0}, g_vec_unroll{0};
 std::atomic<int> g_gather_hints{-1}, g_gather_blocked{-1};
 std::atomic<int> g_staged_lanes{0};
+std::atomic<int> g_vec_smem_pad{0};  // extra dynamic shared memory of the vector swap kernels (see hfk_set_vector_smem_pad)
 
 // ---- copy lanes of the staged mover -------------------------------------------
 // The staged swap hands the link to the copy engines.  One stream executes its copies back to
@@ -230,18 +231,26 @@ static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t s
   if (d->n_blocks == 0) return HFK_OK;
   const SwapArgs a = to_args(d);
   const size_t tables = swap_tables_bytes(swap_id_tile(d->n_blocks), d->layers);
-  if (mover == HFK_MOVER_AUTO) mover = kToHost ? kDefaultMoverOut : kDefaultMoverIn;
   const int64_t items = d->n_blocks * 2 * d->layers;
+  if (mover == HFK_MOVER_AUTO) {
+    // Small launches go to the vector mover: the bulk mover's ring (141.8 KB of shared memory per
+    // CTA) cannot share an SM with a compute kernel's CTA, so each of its launches first waits for
+    // SMs to drain (about 0.14 ms next to a device-filling GEMM) — nothing for a 20 ms swap, half
+    // the time of a 4 MB layer-wise one.  Large launches keep the bulk mover: 4 warps in total.
+    mover = items * d->block_bytes < kAutoBulkMinBytes ? HFK_MOVER_VECTOR
+                                                        : (kToHost ? kDefaultMoverOut : kDefaultMoverIn);
+  }
   if (mover == HFK_MOVER_VECTOR) {
     if (ctas <= 0) ctas = kDefaultSwapCtasVector;
     if (ctas > items) ctas = (int)items;
     const int th = g_vec_threads.load(), un = g_vec_unroll.load();
+    const size_t vsmem = tables + (size_t)g_vec_smem_pad.load();
     cudaError_t e;
-    if (th == 0 || (th == 512 && un == 4)) e = launch_swap_vector<kToHost, 512, 4>(a, ctas, tables, stream);
-    else if (th == 256 && un == 8) e = launch_swap_vector<kToHost, 256, 8>(a, ctas, tables, stream);
-    else if (th == 256 && un == 4) e = launch_swap_vector<kToHost, 256, 4>(a, ctas, tables, stream);
-    else if (th == 1024 && un == 2) e = launch_swap_vector<kToHost, 1024, 2>(a, ctas, tables, stream);
-    else if (th == 128 && un == 8) e = launch_swap_vector<kToHost, 128, 8>(a, ctas, tables, stream);
+    if (th == 0 || (th == 512 && un == 4)) e = launch_swap_vector<kToHost, 512, 4>(a, ctas, vsmem, stream);
+    else if (th == 256 && un == 8) e = launch_swap_vector<kToHost, 256, 8>(a, ctas, vsmem, stream);
+    else if (th == 256 && un == 4) e = launch_swap_vector<kToHost, 256, 4>(a, ctas, vsmem, stream);
+    else if (th == 1024 && un == 2) e = launch_swap_vector<kToHost, 1024, 2>(a, ctas, vsmem, stream);
+    else if (th == 128 && un == 8) e = launch_swap_vector<kToHost, 128, 8>(a, ctas, vsmem, stream);
     else return fail(HFK_ERR_UNSUPPORTED, "swap: vector geometry %dx%d is not compiled", th, un);
     if (e != cudaSuccess) return cuda_fail(e, "kv_swap_vector_kernel launch");
     return HFK_OK;
@@ -384,7 +393,8 @@ static int swap_staged_impl(const hfk_swap_desc *d, const void *slots_host, void
   if (!staging) return fail(HFK_ERR_INVALID_ARG, "swap_staged: staging buffer is null");
   if (!aligned16(staging)) return fail(HFK_ERR_ALIGNMENT, "swap_staged: staging buffer is not 16-byte aligned");
   const int64_t slot_bytes = (int64_t)d->layers * 2 * d->block_bytes;
-  if (d->host_kv_stride != d->block_bytes || d->host_layer_stride != 2 * d->block_bytes)
+  // (a dimension of size 1 never advances, so a one-layer view may carry any layer stride)
+  if (d->host_kv_stride != d->block_bytes || (d->layers > 1 && d->host_layer_stride != 2 * d->block_bytes))
     return fail(HFK_ERR_UNSUPPORTED,
                 "swap_staged: the host pool must be slot-contiguous ([slot][layer][K|V][block])");
   if (d->host_slot_stride < slot_bytes)
@@ -893,6 +903,13 @@ int hfk_enable_peer_access(int peer_device) {
     return HFK_OK;
   }
   if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceEnablePeerAccess");
+  return HFK_OK;
+}
+
+int hfk_set_vector_smem_pad(int bytes) {
+  if (bytes < 0 || bytes > 200 * 1024 || (bytes & 127))
+    return fail(HFK_ERR_INVALID_ARG, "vector smem pad: 0 .. 204800 bytes, multiple of 128");
+  g_vec_smem_pad = bytes;
   return HFK_OK;
 }
 

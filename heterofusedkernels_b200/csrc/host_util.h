@@ -23,6 +23,7 @@ int cuda_fail(cudaError_t e, const char *what);
 constexpr int kDefaultMoverOut = 2;      // HFK_MOVER_BULK
 constexpr int kDefaultMoverIn = 2;       // HFK_MOVER_BULK
 constexpr int kDefaultMoverGather = 2;   // HFK_MOVER_BULK
+constexpr long long kAutoBulkMinBytes = 256ll << 20;  // HFK_MOVER_AUTO: launches below this use the vector mover
 constexpr int kDefaultSwapCtasVector = 16;
 constexpr int kDefaultSwapCtasBulk = 4;
 constexpr int kSwapStageBytes = 16384, kSwapStages = 8, kSwapLag = 2;
@@ -36,8 +37,10 @@ constexpr int kDefaultRowGatherCtas = 32;
 constexpr int kDefaultTransferCtas = 32;
 constexpr int kDefaultRelayoutCtas = 32;
 // Staged swap: copy-engine lanes the slot copies are dealt to, and the largest single copy (a run of
-// consecutive slots is cut at this size so that every lane gets work).
-constexpr int kDefaultStagedLanes = 2;
+// consecutive slots is cut at this size so that every lane gets work).  Measured on the Llama-3-8B
+// step (512 slots of 2 MiB): 1, 2, 3 and 4 lanes all give 50.2 GB/s out / 49.0 in with random slots
+// and 55.7-56.0 / 54.0-54.3 with slots in one run, so the copies stay on the caller's stream.
+constexpr int kDefaultStagedLanes = 1;
 constexpr long long kStagedMaxCopyBytes = 64ll << 20;
 // Block migration: 512-thread CTAs per SM (peer loads over NVLink need megabytes in flight).
 constexpr int kMigrateCtasPerSm = 2;

@@ -86,6 +86,10 @@ int hfk_set_bulk_geometry(int stage_bytes, int n_stages);
  * loads in flight); compiled values 1, 2, 3, 4, 6, 8; 0 restores the default. */
 int hfk_set_bulk_lag(int lag);
 int hfk_set_vector_geometry(int threads, int unroll);
+/* Measurement knob: unused dynamic shared memory added to every CTA of the vector swap kernels
+ * (multiple of 128, up to 200 KiB; 0 = none).  With enough of it a compute kernel's CTAs can no
+ * longer share an SM with a swap CTA, which is how the cost of sharing is measured. */
+int hfk_set_vector_smem_pad(int bytes);
 /* Bulk paged gather: l2_hints bit 0 / bit 1 = loads / stores carry an L2 evict-first policy;
  * blocked = 1 gives every CTA one contiguous run of pages instead of every grid-th page.
  * -1 restores the default of either. */
@@ -245,7 +249,7 @@ int hfk_fused_memcpy_multi_layer_block_transfer_static(void *const *device_layer
  * ======================================================================== */
 
 /* Which data mover a swap uses. */
-#define HFK_MOVER_AUTO 0   /* the entry point's tuned default */
+#define HFK_MOVER_AUTO 0   /* by size: the vector mover for launches below 256 MiB, the bulk mover above */
 #define HFK_MOVER_VECTOR 1 /* 16-byte ld/st loops, whole CTA */
 #define HFK_MOVER_BULK 2   /* one thread per CTA pumping cp.async.bulk through shared memory */
 

@@ -18,10 +18,10 @@ def ops(cuda_device):
     return torch.ops.pcie_through, memory
 
 
-def _filled_cache(device, layers, blocks, bs, heads, hd, dtype, slots, seed=0):
+def _filled_cache(device, layers, blocks, bs, heads, hd, dtype, slots, seed=0, pool_layout="slot_major"):
     from heterofusedkernels_b200.connector import PagedKVCache
 
-    cache = PagedKVCache(layers, blocks, bs, heads, hd, dtype, device, host_slots=slots)
+    cache = PagedKVCache(layers, blocks, bs, heads, hd, dtype, device, host_slots=slots, pool_layout=pool_layout)
     shape = (blocks, bs, heads, hd)
     cpu_k = [o.random_kv_bytes(shape, dtype, seed + 2 * l) for l in range(layers)]
     cpu_v = [o.random_kv_bytes(shape, dtype, seed + 2 * l + 1) for l in range(layers)]
@@ -112,13 +112,17 @@ def test_evict_right_after_a_kernel_wrote_the_blocks_reads_the_new_bytes(ops, cu
 
 
 @pytest.mark.parametrize("group", [1, 3])
-def test_prefetch_and_evict_next_to_a_matmul_loop_are_bit_exact(ops, cuda_device, group):
+@pytest.mark.parametrize("pool_layout,mover", [("slot_major", None), ("slot_major", 2), ("layer_major", None),
+                                               ("layer_major", "staged"), ("slot_major", "staged")])
+def test_prefetch_and_evict_next_to_a_matmul_loop_are_bit_exact(ops, cuda_device, group, pool_layout, mover):
     """Swap-in of the next layers and swap-out of the current ones on the side streams while matmuls run
-    on the main stream; `group` layers per launch.  Checked against the oracle afterwards."""
+    on the main stream; `group` layers per launch; kernel movers and the staged (copy-engine) mover, on
+    both pool layouts.  Checked against the oracle afterwards."""
     from heterofusedkernels_b200.connector import LayerwisePrefetcher
 
     layers, blocks, slots = 6, 64, 96
-    cache, cpu_k, cpu_v = _filled_cache(cuda_device, layers, blocks, 16, 4, 128, o.FP8, slots, seed=11)
+    cache, cpu_k, cpu_v = _filled_cache(cuda_device, layers, blocks, 16, 4, 128, o.FP8, slots, seed=11,
+                                        pool_layout=pool_layout)
     cache.host_pool.view(torch.uint8).copy_(o.random_kv_bytes(tuple(cache.host_pool.shape), o.FP8, 5).view(torch.uint8))
     ref_pool = cache.host_pool.clone()
     pf = LayerwisePrefetcher(cache)
@@ -130,12 +134,14 @@ def test_prefetch_and_evict_next_to_a_matmul_loop_are_bit_exact(ops, cuda_device
     for i, span in enumerate(spans):
         perm = torch.randperm(blocks, generator=torch.Generator().manual_seed(20 + i))
         sl = torch.randperm(slots, generator=torch.Generator().manual_seed(40 + i))
+        if i % 2 == 1:   # every other launch gets its slots as two runs, the way the free list hands them out
+            sl = torch.arange(20 + i, 20 + i + 19)
         plans.append((perm[:10], sl[:10], perm[10:19], sl[10:19]))
     torch.cuda.synchronize()
     for i, span in enumerate(spans):
         in_ids, in_slots, out_ids, out_slots = (t.to(cuda_device) for t in plans[i])
-        pf.prefetch(span, in_ids, in_slots)
-        pf.evict(span, out_ids, out_slots)
+        pf.prefetch(span, in_ids, in_slots, mover=mover, host_slot_ids_cpu=plans[i][1])
+        pf.evict(span, out_ids, out_slots, mover=mover, host_slot_ids_cpu=plans[i][3])
         for _ in range(4 * len(span)):
             torch.matmul(a, b, out=c)
         for l in span:
