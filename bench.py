@@ -694,6 +694,7 @@ class OverlapBench:
         fill_random_bytes(self.cache._k_store, 1)
         fill_random_bytes(self.cache._v_store, 2)
         self.pf = LayerwisePrefetcher(self.cache)
+        self.pf_serial = LayerwisePrefetcher(self.cache, one_stream=True)
         self.a = torch.randn(8192, 3584, device=device, dtype=torch.bfloat16)
         self.b = torch.randn(3584, 18944, device=device, dtype=torch.bfloat16)
         self.c = torch.empty(8192, 18944, device=device, dtype=torch.bfloat16)
@@ -744,7 +745,11 @@ class OverlapBench:
         """One pass over all layers.  kind: None (the prefetcher's shipped defaults), "vector" or
         "vector@<threads>x<loads in flight>[+pad<KiB of unused shared memory>]", "bulk" or "bulk@<stage bytes>x<stages>[+lag<k>]", "staged"
         (packing kernel + copy-engine transfers) or "copy_engine" (one copy per chunk)."""
-        pkg, pf, cache, L = self.pkg, self.pf, self.cache, self.L
+        pkg, cache, L = self.pkg, self.cache, self.L
+        serial = bool(kind) and kind.endswith("+serial")
+        pf = self.pf_serial if serial else self.pf
+        if serial:
+            kind = kind[:-len("+serial")] or None
         lib = pkg.capi.lib()
         base_kind = (kind or "").split("@")[0].split("+")[0]
         mv = {"": None, "vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK, "staged": "staged",
@@ -826,8 +831,16 @@ class OverlapBench:
 
         in_gbs, in_ms = rate(ev_in)
         out_gbs, out_ms = rate(ev_out)
+        # both directions of a group together: bytes both ways over first start .. last end
+        pair = None
+        if len(ev_in) == len(ev_out) and ev_in:
+            per = []
+            for (a_i, b_i, n_i), (a_o, b_o, n_o) in zip(ev_in, ev_out):
+                span = max(x.elapsed_time(y) for x in (a_i, a_o) for y in (b_i, b_o))
+                per.append((n_i + n_o) * self.layer_bytes / (span * 1e-3) / GB)
+            pair = statistics.median(per)
         return {"main_ms": e0.elapsed_time(e1), "in_gbs": in_gbs, "out_gbs": out_gbs, "in_ms_median": in_ms,
-                "out_ms_median": out_ms, "launches": len(ev_in) + len(ev_out)}
+                "out_ms_median": out_ms, "pair_gbs": pair, "launches": len(ev_in) + len(ev_out)}
 
     def verify(self, group: int) -> dict:
         """Every block a swap-in wrote equals its slot and every slot a swap-out wrote equals its block,
@@ -853,13 +866,15 @@ class OverlapBench:
         med_main = statistics.median(r["main_ms"] for r in runs)
         ver = self.verify(group)
         return {"mover": kind or "default", "ctas_per_direction": ctas or "default", "layers_per_launch": group,
-                "pool_layout": self.pool_layout, "slots": "runs" if self.slot_runs else "random",
+                "side_streams": 1 if (kind or "").endswith("+serial") else 2, "pool_layout": self.pool_layout, "slots": "runs" if self.slot_runs else "random",
                 "gemm_ms_alone": t_a, "gemm_ms_overlapped": med_main,
                 "gemm_slowdown_pct": 100.0 * (med_main / t_a - 1.0),
                 "gemm_tflops_alone": self.L * self.flops / (t_a * 1e-3) / 1e12,
                 "swap_in_gbs": statistics.median(r["in_gbs"] for r in runs),
                 "swap_out_gbs": statistics.median(r["out_gbs"] for r in runs),
                 "swap_in_gbs_no_gemm": solo["in_gbs"], "swap_out_gbs_no_gemm": solo["out_gbs"],
+                "both_directions_gbs": statistics.median(r["pair_gbs"] for r in runs) if runs[0]["pair_gbs"] else None,
+                "both_directions_gbs_no_gemm": solo["pair_gbs"],
                 "launches_per_pass": runs[0]["launches"], "verified": ver["verified"],
                 "bytes_checked": ver["bytes_checked"]}
 
@@ -923,11 +938,10 @@ def bench_overlap(g, device, args, pkg) -> dict:
     sampler = ClockSampler(device.index or 0)
     reps = args.overlap_reps
     variants = []
-    table = [(None, None, 1), (None, None, 2), (None, None, 4), (None, None, 8),
-             ("vector", 16, 8), ("vector+pad96", 16, 4), ("vector+pad96", 16, 8), ("vector+pad96", 8, 8),
-             ("vector+pad160", 32, 8), ("bulk", 16, 8), ("bulk", 8, 8),
-             ("vector@256x8", 32, 4), ("vector@128x8", 64, 4),
-             ("bulk@2048x4", 64, 4), ("bulk@2048x4+lag1", 64, 4), ("bulk@4096x4+lag1", 32, 4)]
+    table = [(None, None, 1), (None, None, 4), (None, None, 8),
+             ("+serial", None, 1), ("+serial", None, 2), ("+serial", None, 4), ("+serial", None, 8),
+             ("vector@256x8+serial", 32, 4), ("bulk+serial", 8, 8), ("bulk@2048x4+serial", 64, 4),
+             ("vector+pad96", 16, 8), ("bulk", 8, 8), ("vector@256x8", 32, 4), ("bulk@2048x4", 64, 4)]
     if args.overlap_quick:
         table = table[:2]
     for kind, ctas, group in table:

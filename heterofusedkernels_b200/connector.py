@@ -375,10 +375,15 @@ class LayerwisePrefetcher:
     DEFAULT_AIV = 16
     DEFAULT_MOVER = _pkg.capi.MOVER_VECTOR
 
-    def __init__(self, cache: PagedKVCache):
+    def __init__(self, cache: PagedKVCache, one_stream: bool = False):
+        """``one_stream=True`` issues swap-ins and swap-outs on ONE side stream, so the two directions
+        never cross the link at the same time: each then runs at the full one-direction rate.  With two
+        streams (the default) the pair finishes a little sooner, but next to a device-filling GEMM the
+        swap-in falls to about half its rate while the swap-out keeps its own (the upstream lanes carry
+        the swap-out's writes and the swap-in's read requests)."""
         self.cache = cache
         self.in_stream = torch.cuda.Stream(device=cache.device, priority=-1)
-        self.out_stream = torch.cuda.Stream(device=cache.device, priority=-1)
+        self.out_stream = self.in_stream if one_stream else torch.cuda.Stream(device=cache.device, priority=-1)
         self.ready = [torch.cuda.Event() for _ in range(cache.layers)]
         self.evicted = [torch.cuda.Event() for _ in range(cache.layers)]
         self._staging: Dict[str, torch.Tensor] = {}
