@@ -693,8 +693,8 @@ class OverlapBench:
                                   host_raw=host_raw, pool_layout=pool_layout)
         fill_random_bytes(self.cache._k_store, 1)
         fill_random_bytes(self.cache._v_store, 2)
-        self.pf = LayerwisePrefetcher(self.cache)
-        self.pf_serial = LayerwisePrefetcher(self.cache, one_stream=True)
+        self.pf = LayerwisePrefetcher(self.cache)                       # shipped default: one side stream
+        self.pf_two = LayerwisePrefetcher(self.cache, one_stream=False)
         self.a = torch.randn(8192, 3584, device=device, dtype=torch.bfloat16)
         self.b = torch.randn(3584, 18944, device=device, dtype=torch.bfloat16)
         self.c = torch.empty(8192, 18944, device=device, dtype=torch.bfloat16)
@@ -746,10 +746,10 @@ class OverlapBench:
         "vector@<threads>x<loads in flight>[+pad<KiB of unused shared memory>]", "bulk" or "bulk@<stage bytes>x<stages>[+lag<k>]", "staged"
         (packing kernel + copy-engine transfers) or "copy_engine" (one copy per chunk)."""
         pkg, cache, L = self.pkg, self.cache, self.L
-        serial = bool(kind) and kind.endswith("+serial")
-        pf = self.pf_serial if serial else self.pf
-        if serial:
-            kind = kind[:-len("+serial")] or None
+        two = bool(kind) and kind.endswith("+2streams")
+        pf = self.pf_two if two else self.pf
+        if two:
+            kind = kind[:-len("+2streams")] or None
         lib = pkg.capi.lib()
         base_kind = (kind or "").split("@")[0].split("+")[0]
         mv = {"": None, "vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK, "staged": "staged",
@@ -866,7 +866,7 @@ class OverlapBench:
         med_main = statistics.median(r["main_ms"] for r in runs)
         ver = self.verify(group)
         return {"mover": kind or "default", "ctas_per_direction": ctas or "default", "layers_per_launch": group,
-                "side_streams": 1 if (kind or "").endswith("+serial") else 2, "pool_layout": self.pool_layout, "slots": "runs" if self.slot_runs else "random",
+                "side_streams": 2 if (kind or "").endswith("+2streams") else 1, "pool_layout": self.pool_layout, "slots": "runs" if self.slot_runs else "random",
                 "gemm_ms_alone": t_a, "gemm_ms_overlapped": med_main,
                 "gemm_slowdown_pct": 100.0 * (med_main / t_a - 1.0),
                 "gemm_tflops_alone": self.L * self.flops / (t_a * 1e-3) / 1e12,
@@ -920,7 +920,8 @@ def overlap_summary(ob: OverlapBench, reps: int, group: int) -> dict:
     m = ob.measure(None, None, group, reps)
     clocks = sampler.stop()
     status = ob.cache.status()
-    return {"workload": "qwen2_7b_fp8_prefetch", "mover": "LayerwisePrefetcher defaults (vector mover, 16 CTAs per direction)",
+    return {"workload": "qwen2_7b_fp8_prefetch",
+            "mover": "LayerwisePrefetcher defaults (bulk mover, 2 KiB x 4 ring, 64 CTAs, one side stream)",
             "layers_per_launch": group, "gemm_slowdown_pct": m["gemm_slowdown_pct"], "swap_in_gbs": m["swap_in_gbs"],
             "swap_out_gbs": m["swap_out_gbs"], "swap_in_gbs_no_gemm": m["swap_in_gbs_no_gemm"],
             "swap_out_gbs_no_gemm": m["swap_out_gbs_no_gemm"], "gemm_tflops": m["gemm_tflops_alone"],
@@ -938,17 +939,17 @@ def bench_overlap(g, device, args, pkg) -> dict:
     sampler = ClockSampler(device.index or 0)
     reps = args.overlap_reps
     variants = []
-    table = [(None, None, 1), (None, None, 4), (None, None, 8),
-             ("+serial", None, 1), ("+serial", None, 2), ("+serial", None, 4), ("+serial", None, 8),
-             ("vector@256x8+serial", 32, 4), ("bulk+serial", 8, 8), ("bulk@2048x4+serial", 64, 4),
-             ("vector+pad96", 16, 8), ("bulk", 8, 8), ("vector@256x8", 32, 4), ("bulk@2048x4", 64, 4)]
+    table = [(None, None, 1), (None, None, 2), (None, None, 4), (None, None, 8),
+             ("+2streams", None, 1), ("+2streams", None, 4),
+             ("bulk", 32, 4), ("bulk", 128, 4), ("bulk@2048x8", 32, 4), ("bulk@4096x4", 32, 4), ("bulk@16384x8", 8, 8),
+             ("vector", 16, 4), ("vector@256x8", 32, 4), ("vector@128x8", 64, 4), ("vector+2streams", 16, 4)]
     if args.overlap_quick:
         table = table[:2]
     for kind, ctas, group in table:
         variants.append(ob.measure(kind, ctas, group, reps))
     stamps = []
     for kind, ctas in (() if args.overlap_quick else
-                       (("bulk", 4), ("bulk@2048x4", 64), ("bulk@4096x4+lag1", 64), ("vector", 16), ("vector@128x8", 64))):
+                       ((None, None), ("bulk@4096x4", 32), ("bulk@16384x8", 4), ("vector", 16), ("vector@256x8", 32))):
         for direction in ("in", "out"):
             stamps.append(ob.stamps(kind, ctas, 1, direction))
     status = ob.cache.status()
@@ -957,7 +958,7 @@ def bench_overlap(g, device, args, pkg) -> dict:
     # the same pipeline on a layer-major pool with slots handed out as runs: one copy-engine transfer per
     # layer and direction (staged), next to the kernel movers on the same layout
     ob = OverlapBench(g, device, pkg, pool_layout="layer_major", slot_runs=True)
-    for kind, ctas, group in (("staged", None, 1), ("staged", None, 4), ("staged@2048x4", 64, 4), (None, None, 4)):
+    for kind, ctas, group in (("staged", None, 4), ("staged@2048x4", 64, 4), (None, None, 4)):
         variants.append(ob.measure(kind, ctas, group, reps))
     clocks = sampler.stop()
     status |= ob.cache.status()

@@ -213,7 +213,9 @@ static SwapArgs to_args(const hfk_swap_desc *d) {
   return a;
 }
 
-static int swap_id_tile(int64_t n_blocks) { return (int)std::min<int64_t>(std::max<int64_t>(n_blocks, 1), kSwapIdTile); }
+static int swap_id_tile(int64_t n_blocks, int cap = kSwapIdTile) {
+  return (int)std::min<int64_t>(std::max<int64_t>(n_blocks, 1), cap);
+}
 
 template <bool kToHost, int kThreads, int kUnroll>
 static cudaError_t launch_swap_vector(const SwapArgs &a, int ctas, size_t smem, cudaStream_t s) {
@@ -230,17 +232,10 @@ static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t s
   if (rc != HFK_OK) return rc;
   if (d->n_blocks == 0) return HFK_OK;
   const SwapArgs a = to_args(d);
-  const size_t tables = swap_tables_bytes(swap_id_tile(d->n_blocks), d->layers);
   const int64_t items = d->n_blocks * 2 * d->layers;
-  if (mover == HFK_MOVER_AUTO) {
-    // Small launches go to the vector mover: the bulk mover's ring (141.8 KB of shared memory per
-    // CTA) cannot share an SM with a compute kernel's CTA, so each of its launches first waits for
-    // SMs to drain (about 0.14 ms next to a device-filling GEMM) — nothing for a 20 ms swap, half
-    // the time of a 4 MB layer-wise one.  Large launches keep the bulk mover: 4 warps in total.
-    mover = items * d->block_bytes < kAutoBulkMinBytes ? HFK_MOVER_VECTOR
-                                                        : (kToHost ? kDefaultMoverOut : kDefaultMoverIn);
-  }
+  if (mover == HFK_MOVER_AUTO) mover = kToHost ? kDefaultMoverOut : kDefaultMoverIn;
   if (mover == HFK_MOVER_VECTOR) {
+    const size_t tables = swap_tables_bytes(swap_id_tile(d->n_blocks), d->layers);
     if (ctas <= 0) ctas = kDefaultSwapCtasVector;
     if (ctas > items) ctas = (int)items;
     const int th = g_vec_threads.load(), un = g_vec_unroll.load();
@@ -256,15 +251,25 @@ static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t s
     return HFK_OK;
   }
   if (mover == HFK_MOVER_BULK) {
-    const BulkPlan p = plan_bulk(d->block_bytes, tables, kSwapStageBytes, kSwapStages, kSwapLag);
-    if (ctas <= 0) ctas = kDefaultSwapCtasBulk;
+    // Two rings, chosen by the bytes of the launch.  A launch of a few MB (a layer-wise swap next to
+    // a running compute kernel) gets many CTAs with a ring small enough to share an SM with a compute
+    // CTA (a bf16 GEMM of cuBLAS leaves about 19 KB of shared memory and 22 K registers per SM): they
+    // start within 10 us where a CTA that needs an SM of its own waits about 140 us for one to drain.
+    // A large launch gets 4 CTAs with a 128 KiB ring each: the wait is nothing against 20 ms, and the
+    // whole transfer costs 4 warps.
+    const bool small = items * d->block_bytes < kAutoBulkMinBytes;
+    const int id_tile = swap_id_tile(d->n_blocks, small ? kSwapSmallIdTile : kSwapIdTile);
+    const size_t tables = swap_tables_bytes(id_tile, d->layers);
+    const BulkPlan p = small ? plan_bulk(d->block_bytes, tables, kSwapSmallStageBytes, kSwapSmallStages, kSwapLag)
+                             : plan_bulk(d->block_bytes, tables, kSwapStageBytes, kSwapStages, kSwapLag);
+    if (ctas <= 0) ctas = small ? kDefaultSwapCtasBulkSmall : kDefaultSwapCtasBulk;
     const int64_t pieces = (d->block_bytes + p.stage_bytes - 1) / p.stage_bytes;
     if (ctas > items * pieces) ctas = (int)(items * pieces);
     cudaError_t e = launch_by_lag(p.lag, [&](auto lag) {
       auto k = kv_swap_bulk_kernel<kToHost, decltype(lag)::value>;
       cudaError_t err = allow_smem(k, p.smem);
       if (err != cudaSuccess) return err;
-      k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, swap_id_tile(a.n_blocks));
+      k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, id_tile);
       return cudaGetLastError();
     });
     if (e != cudaSuccess) return cuda_fail(e, "kv_swap_bulk_kernel launch");

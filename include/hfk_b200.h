@@ -249,7 +249,7 @@ int hfk_fused_memcpy_multi_layer_block_transfer_static(void *const *device_layer
  * ======================================================================== */
 
 /* Which data mover a swap uses. */
-#define HFK_MOVER_AUTO 0   /* by size: the vector mover for launches below 256 MiB, the bulk mover above */
+#define HFK_MOVER_AUTO 0   /* the bulk mover; its ring and CTA count follow the bytes of the launch */
 #define HFK_MOVER_VECTOR 1 /* 16-byte ld/st loops, whole CTA */
 #define HFK_MOVER_BULK 2   /* one thread per CTA pumping cp.async.bulk through shared memory */
 

@@ -121,6 +121,22 @@ SWAP_SHAPES = [
 @pytest.mark.parametrize("mover", MOVERS)
 @pytest.mark.parametrize("shape", SWAP_SHAPES, ids=[str(i) for i in range(len(SWAP_SHAPES))])
 def test_swap_out_and_in_shapes_layouts_and_id_types(hfk, cuda_device, mover, shape):
+    _swap_round_trip(hfk, cuda_device, mover, shape)
+
+
+@pytest.mark.parametrize("ring", [(16384, 8), (32768, 3), (128, 2)], ids=["16Kx8", "32Kx3", "128x2"])
+@pytest.mark.parametrize("shape", SWAP_SHAPES, ids=[str(i) for i in range(len(SWAP_SHAPES))])
+def test_swap_with_the_ring_of_large_launches_forced(hfk, cuda_device, ring, shape):
+    """Launches below 256 MiB take the small ring by default; the ring that 1 GB launches use (and two
+    extreme ones) is forced here so that it sees the small shapes too."""
+    hfk.check(hfk.lib().hfk_set_bulk_geometry(*ring), "hfk_set_bulk_geometry")
+    try:
+        _swap_round_trip(hfk, cuda_device, 2, shape)
+    finally:
+        hfk.lib().hfk_set_bulk_geometry(0, 0)
+
+
+def _swap_round_trip(hfk, cuda_device, mover, shape):
     layers, blocks, chunk, dtype, nslots, n, layout, pad, idt = shape
     case = SwapCase(hfk, cuda_device, layers, blocks, chunk, dtype, nslots, seed=11, pool_layout=layout,
                     block_pad=pad)
