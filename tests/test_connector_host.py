@@ -64,3 +64,17 @@ def test_random_requests_never_share_a_slot():
         assert p.free_count == 500 - len(in_use) == sum(n for _, n in p.runs())
         runs = p.runs()
         assert all(runs[i][0] + runs[i][1] < runs[i + 1][0] for i in range(len(runs) - 1))   # sorted, never adjacent
+
+
+def test_the_connector_takes_the_staged_mover_only_for_host_resident_slot_lists_made_of_runs():
+    from heterofusedkernels_b200.connector import PagedKVCache
+
+    c = PagedKVCache.__new__(PagedKVCache)       # the choice needs no device state
+    c.pool_layout = "slot_major"
+    assert c._pick_mover(torch.arange(100, 612)) == "staged"                       # one run
+    assert c._pick_mover(list(range(5, 13)) + list(range(40, 48))) == "staged"     # two runs of 8
+    assert c._pick_mover(torch.randperm(40000, generator=torch.Generator().manual_seed(0))[:512]) is None
+    assert c._pick_mover(torch.tensor([0, 1, 2, 3, 10, 11, 12, 13, 20, 22])) is None   # mean run below 4
+    assert c._pick_mover([1, 2, 3]) is None                                        # too few to matter
+    c.pool_layout = "layer_major"                                                  # slots are not contiguous there
+    assert c._pick_mover(torch.arange(64)) is None
