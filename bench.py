@@ -344,14 +344,18 @@ class SwapBench:
     # one call each way; ids: device tensors (value leg) or pinned host tensors (e2e leg)
     def _out(self, ids, slots, slots_cpu):
         self.launches += 1
-        if self.mover == "staged":
+        if isinstance(self.mover, str) and self.mover.startswith("hybrid"):
+            self.cache.swap_out(ids, slots_cpu, aiv=self.aiv, mover=self.mover)
+        elif self.mover == "staged":
             self.cache.swap_out_staged(ids, slots_cpu, staging_bytes=self.staging_bytes, aiv=self.aiv)
         else:
             self.cache.swap_out(ids, slots, aiv=self.aiv, mover=self.mover)
 
     def _in(self, ids, slots, slots_cpu):
         self.launches += 1
-        if self.mover == "staged":
+        if isinstance(self.mover, str) and self.mover.startswith("hybrid"):
+            self.cache.swap_in(ids, slots_cpu, aiv=self.aiv, mover=self.mover)
+        elif self.mover == "staged":
             self.cache.swap_in_staged(ids, slots_cpu, staging_bytes=self.staging_bytes, aiv=self.aiv)
         else:
             self.cache.swap_in(ids, slots, aiv=self.aiv, mover=self.mover)
@@ -1324,6 +1328,10 @@ def main() -> None:
             r = timed_leg(sb, variant, args.steps, args.warmup, e2e=False)
             sb.mover = mover
             lib.hfk_set_staged_copy_lanes(args.staged_lanes)
+        elif var.startswith("mover=hybrid"):
+            sb.mover = var.split("=")[1]
+            r = timed_leg(sb, variant, args.steps, args.warmup, e2e=False)
+            sb.mover = mover
         elif var.startswith("mover="):
             sb.mover = {"vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK}[var.split("=")[1]]
             r = timed_leg(sb, variant, args.steps, args.warmup, e2e=False)

@@ -119,14 +119,18 @@ class PagedKVCache:
 
     ``swap_out`` / ``swap_in`` take ``mover`` = one of ``capi.MOVER_*`` (a kernel crosses the
     link) or ``"staged"`` (a packing kernel plus copy-engine transfers; needs the slot ids on
-    the host, which is where a scheduler has them).  ``mover=None`` decides per call: when the
-    slot ids are on the host and come in runs of ``STAGED_MIN_RUN`` or more consecutive slots on
-    average (what the free list hands out), the staged mover is taken — the copy engine crosses
-    PCIe in 256-byte transactions and a kernel in 128-byte ones, measured on the Llama-3-8B step
-    as 55.2 GB/s against 52.0 once copies are 8 MiB or larger (2 MiB copies: 49.7) — otherwise
-    the library's kernel default.
+    the host, which is where a scheduler has them) or ``"hybrid[:fraction]"`` (that fraction of
+    the blocks staged and the rest by the kernel, both at the same time).  ``mover=None`` decides
+    per call, from what the copy engine and a kernel do on PCIe (256-byte against 128-byte
+    transactions; Llama-3-8B step, 2 MiB slots): slot ids on the host in runs of
+    ``STAGED_MIN_RUN`` or more consecutive slots on average (what the free list hands out) →
+    staged, 55.2 GB/s against the kernels' 52.0; slot ids on the host, scattered, and at least
+    ``HYBRID_MIN_BYTES`` to move → hybrid, 53.5 GB/s (the kernel's traffic fills the gaps between
+    the copy engine's 2 MiB copies, which alone reach 49.7); anything else → the kernels.
     """
     STAGED_MIN_RUN = 4
+    HYBRID_FRACTION = 0.4            # share of a "hybrid" swap that goes through the copy engine
+    HYBRID_MIN_BYTES = 128 << 20
 
     def __init__(self, layers: int, num_blocks: int, block_size: int, kv_heads: int, head_dim: int,
                  dtype: torch.dtype, device: torch.device | str = "cuda", host_slots: int = 0,
@@ -163,7 +167,8 @@ class PagedKVCache:
         self.host_pool: Optional[torch.Tensor] = None
         self._host_raw: Optional[torch.Tensor] = None
         self.slot_pool: Optional[HostSlotPool] = None
-        self._staging_buf: Optional[torch.Tensor] = None
+        self._staging_bufs: Dict[str, torch.Tensor] = {}      # one staging buffer per direction
+        self._hybrid_streams: Dict[str, Tuple[torch.cuda.Stream, torch.cuda.Stream]] = {}
         if host_raw is not None:
             self.attach_host_raw(host_raw, host_slots)
         elif host_slots > 0:
@@ -214,7 +219,9 @@ class PagedKVCache:
                 return None
             s = torch.tensor(list(host_slot_ids), dtype=torch.int64)
         runs = 1 + int((s[1:] - s[:-1] != 1).sum())
-        return "staged" if s.numel() >= self.STAGED_MIN_RUN * runs else None
+        if s.numel() >= self.STAGED_MIN_RUN * runs:
+            return "staged"
+        return "hybrid" if s.numel() * self.slot_bytes >= self.HYBRID_MIN_BYTES else None
 
     @staticmethod
     def _cpu_ids(ids) -> torch.Tensor:
@@ -236,6 +243,9 @@ class PagedKVCache:
             mover = self._pick_mover(host_slot_ids)
         if mover == "staged":
             self.swap_out_staged(device_block_ids, self._cpu_ids(host_slot_ids), aiv=aiv)
+        elif isinstance(mover, str) and mover.startswith("hybrid"):
+            self._hybrid(True, device_block_ids, host_slot_ids, aiv,
+                         float(mover.split(":")[1]) if ":" in mover else self.HYBRID_FRACTION)
         else:
             torch.ops.pcie_through.swap_out(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
                                             self._ids(host_slot_ids), self.num_blocks, None, aiv, mover)
@@ -250,6 +260,9 @@ class PagedKVCache:
             mover = self._pick_mover(host_slot_ids)
         if mover == "staged":
             self.swap_in_staged(device_block_ids, self._cpu_ids(host_slot_ids), aiv=aiv)
+        elif isinstance(mover, str) and mover.startswith("hybrid"):
+            self._hybrid(False, device_block_ids, host_slot_ids, aiv,
+                         float(mover.split(":")[1]) if ":" in mover else self.HYBRID_FRACTION)
         else:
             torch.ops.pcie_through.swap_in(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
                                            self._ids(host_slot_ids), self.num_blocks, None, aiv, mover)
@@ -259,11 +272,45 @@ class PagedKVCache:
     def release(self, host_slot_ids) -> None:
         self.slot_pool.free(self._cpu_ids(host_slot_ids))
 
-    def _staging(self, staging_bytes: int) -> torch.Tensor:
+    def _staging(self, direction: str, staging_bytes: int) -> torch.Tensor:
+        """The staging buffer of one direction ("out" / "in").  Swap-outs and swap-ins may run at the same
+        time (each has its own buffer); two staged or hybrid swaps of the SAME direction share one and
+        must be ordered by the caller (one stream, or events)."""
         want = max(self.slot_bytes, staging_bytes)
-        if self._staging_buf is None or self._staging_buf.numel() < want:
-            self._staging_buf = torch.empty(want, dtype=torch.uint8, device=self.device)
-        return self._staging_buf
+        buf = self._staging_bufs.get(direction)
+        if buf is None or buf.numel() < want:
+            buf = self._staging_bufs[direction] = torch.empty(want, dtype=torch.uint8, device=self.device)
+        return buf
+
+    def _hybrid(self, out: bool, device_block_ids, host_slot_ids, aiv: Optional[int], fraction: float) -> None:
+        """One swap split between the two ways across the link, running at the same time: the first
+        `fraction` of the blocks through the staged mover (copy engine) on one internal stream, the rest
+        through the kernel on another; both fork from the current stream and join it again."""
+        cur = torch.cuda.current_stream(self.device)
+        direction = "out" if out else "in"
+        if direction not in self._hybrid_streams:
+            self._hybrid_streams[direction] = (torch.cuda.Stream(self.device), torch.cuda.Stream(self.device))
+        s_copy, s_kernel = self._hybrid_streams[direction]
+        slots_cpu = self._cpu_ids(host_slot_ids)
+        dev_ids, slots_dev = self._ids(device_block_ids), self._ids(host_slot_ids)
+        n = dev_ids.numel()
+        k = max(0, min(n, int(round(n * fraction))))
+        fork = torch.cuda.Event()
+        fork.record(cur)
+        if k > 0:
+            s_copy.wait_event(fork)
+            with torch.cuda.stream(s_copy):
+                (self.swap_out_staged if out else self.swap_in_staged)(dev_ids[:k], slots_cpu[:k], aiv=aiv)
+            cur.wait_stream(s_copy)
+        if k < n:
+            s_kernel.wait_event(fork)
+            op = torch.ops.pcie_through.swap_out if out else torch.ops.pcie_through.swap_in
+            with torch.cuda.stream(s_kernel):
+                op(self.k_ptrs, self.v_ptrs, self.host_pool, dev_ids[k:], slots_dev[k:], self.num_blocks, None, aiv, None)
+            cur.wait_stream(s_kernel)
+        for t in (dev_ids, slots_dev):
+            t.record_stream(s_copy)
+            t.record_stream(s_kernel)
 
     def swap_out_staged(self, device_block_ids, host_slot_ids_cpu: torch.Tensor, staging_bytes: int = 256 << 20,
                         aiv: Optional[int] = None) -> None:
@@ -271,13 +318,13 @@ class PagedKVCache:
         cudaMemcpyAsync per run of consecutive host slots (256-byte PCIe transactions instead of a
         kernel's 128-byte ones)."""
         torch.ops.pcie_through.swap_out_staged(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
-                                               host_slot_ids_cpu, self._staging(staging_bytes), self.num_blocks,
+                                               host_slot_ids_cpu, self._staging("out", staging_bytes), self.num_blocks,
                                                None, aiv)
 
     def swap_in_staged(self, device_block_ids, host_slot_ids_cpu: torch.Tensor, staging_bytes: int = 256 << 20,
                        aiv: Optional[int] = None) -> None:
         torch.ops.pcie_through.swap_in_staged(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
-                                              host_slot_ids_cpu, self._staging(staging_bytes), self.num_blocks,
+                                              host_slot_ids_cpu, self._staging("in", staging_bytes), self.num_blocks,
                                               None, aiv)
 
     def swap_out_copy_engine(self, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor) -> None:

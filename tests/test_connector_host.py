@@ -71,10 +71,14 @@ def test_the_connector_takes_the_staged_mover_only_for_host_resident_slot_lists_
 
     c = PagedKVCache.__new__(PagedKVCache)       # the choice needs no device state
     c.pool_layout = "slot_major"
+    c.slot_bytes = 2 << 20
     assert c._pick_mover(torch.arange(100, 612)) == "staged"                       # one run
     assert c._pick_mover(list(range(5, 13)) + list(range(40, 48))) == "staged"     # two runs of 8
-    assert c._pick_mover(torch.randperm(40000, generator=torch.Generator().manual_seed(0))[:512]) is None
-    assert c._pick_mover(torch.tensor([0, 1, 2, 3, 10, 11, 12, 13, 20, 22])) is None   # mean run below 4
+    scattered = torch.randperm(40000, generator=torch.Generator().manual_seed(0))[:512]
+    assert c._pick_mover(scattered) == "hybrid"                                    # 1 GiB of scattered 2 MiB slots
+    assert c._pick_mover(scattered[:32]) is None                                   # 64 MiB: not worth two movers
+    assert c._pick_mover(scattered.to(torch.int64).tolist()[:10]) is None
+    assert c._pick_mover(torch.tensor([0, 1, 2, 3, 10, 11, 12, 13, 20, 22])) is None   # mean run below 4, small
     assert c._pick_mover([1, 2, 3]) is None                                        # too few to matter
     c.pool_layout = "layer_major"                                                  # slots are not contiguous there
     assert c._pick_mover(torch.arange(64)) is None

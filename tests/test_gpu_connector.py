@@ -77,6 +77,22 @@ def test_swaps_driven_by_the_slot_allocator_and_the_staged_copy_lanes(ops, cuda_
         lib.hfk_set_staged_copy_lanes(0)
 
 
+@pytest.mark.parametrize("fraction", ["0.5", "0.0", "1.0", "0.37"])
+def test_hybrid_mover_splits_a_swap_between_copy_engine_and_kernel(ops, cuda_device, fraction):
+    cache, cpu_k, cpu_v = _filled_cache(cuda_device, 3, 64, 16, 2, 64, torch.bfloat16, 96, seed=13)
+    ref_pool = torch.zeros_like(cache.host_pool)
+    ids, slots, back = o.distinct_ids(41, 64, 1), o.distinct_ids(41, 96, 2), o.distinct_ids(41, 64, 3)
+    cache.swap_out(ids, slots, mover="hybrid:" + fraction)
+    cache.swap_in(back, slots, mover="hybrid:" + fraction)
+    o.swap_out(cpu_k, cpu_v, ref_pool, ids, slots)
+    o.swap_in(cpu_k, cpu_v, ref_pool, back, slots)
+    torch.cuda.synchronize()
+    assert torch.equal(u8(cache.host_pool), u8(ref_pool))
+    for d, c in zip(cache.k_caches + cache.v_caches, cpu_k + cpu_v):
+        assert torch.equal(u8(d.cpu()), u8(c))
+    assert cache.status() == 0
+
+
 def test_evict_right_after_a_kernel_wrote_the_blocks_reads_the_new_bytes(ops, cuda_device):
     """No global synchronisation: the main stream is kept busy, then writes the blocks, and evict is
     issued immediately.  The swap-out stream must wait for the writes."""
