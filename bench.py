@@ -1315,8 +1315,10 @@ def main() -> None:
     e2e = {"value": e2["value"], "unit": "GB/s", "ms_per_step": e2["ms_per_step"],
            "h2d_bytes_per_step": g.swap_bytes + id_bytes, "d2h_bytes_per_step": g.swap_bytes + 4,
            "verified": e2["all_verified"],
-           "api": "PagedKVCache.swap_out/swap_in -> torch.ops.pcie_through.swap_out/swap_in; payload moves "
-                  "between HBM and the pinned host pool inside the timed region"}
+           "api": "PagedKVCache.swap_out/swap_in -> torch.ops.pcie_through.*; payload moves between HBM and the "
+                  "pinned host pool inside the timed region",
+           "mover": ("picked by the connector from the host-resident id lists: " +
+                     str(cache._pick_mover(sb.pin_sets[1][1]) or "kernels")) if mover is None else args.mover}
 
     # ---- optional extra variants on the same state ---------------------------------------------
     extra = {}
@@ -1426,6 +1428,7 @@ def main() -> None:
                 "swap_out_achieved": out_gbs, "swap_out_peak": pcie["d2h"], "swap_out_frac": out_gbs / pcie["d2h"],
                 "swap_in_achieved": in_gbs, "swap_in_peak": pcie["h2d"], "swap_in_frac": in_gbs / pcie["h2d"],
                 "nominal_gen5_x16": 63.0, "algorithmic_bytes_per_launch": g.swap_bytes,
+                "e2e_per_gpu": e2["value"] / world, "e2e_frac": e2["value"] / world / pcie_peak,
                 "verified": bool(val["all_verified"] and e2["all_verified"])}
     for k, v in tried.items():
         if k != variant:
