@@ -75,3 +75,43 @@ def test_ranks_are_spread_over_the_visible_gpus():
     assert [ranks.spread_device_index(r, 8, 8) for r in range(8)] == list(range(8))
     assert [ranks.spread_device_index(r, 2, 2) for r in range(2)] == [0, 1]
     assert ranks.spread_device_index(0, 1, 8) == 0 and ranks.spread_device_index(3, 4, 1) == 0
+
+
+def test_id_sets_let_a_step_read_the_previous_steps_slots_while_it_writes_its_own():
+    sets = ranks.rank_id_sets(3, 6, 50, 200, 120)
+    prev = None
+    for out_ids, slots, in_ids in sets:
+        assert not set(out_ids.tolist()) & set(in_ids.tolist())          # blocks come back to OTHER blocks
+        assert len(set(slots.tolist())) == 50 == slots.numel()
+        if prev is not None:
+            assert not set(slots.tolist()) & prev                         # consecutive steps: disjoint slots
+        prev = set(slots.tolist())
+    with pytest.raises(AssertionError):
+        ranks.rank_id_sets(0, 2, 50, 99, 120)                             # cache too small for disjoint lists
+
+
+def test_issue_orders_of_a_step_per_rank():
+    """How each rank issues a step under every variant of the benchmark (no GPU: only the plan)."""
+    import sys
+    from pathlib import Path
+    from types import SimpleNamespace as NS
+
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+
+    def plan(rank, world, variant):
+        sb = bench.SwapBench.__new__(bench.SwapBench)
+        sb.ctx = NS(rank=rank, world=world)
+        return sb.plan(variant)
+
+    assert plan(0, 1, "sequential") == ("own", "out_first", 1, False)
+    assert plan(1, 2, "sequential") == ("own", "out_first", 1, False)
+    assert plan(0, 2, "stagger") == ("own", "out_first", 1, False)
+    assert plan(1, 2, "stagger") == ("prev", "in_first", 1, False)        # odd ranks swap in first
+    assert plan(0, 8, "bidir") == plan(5, 8, "bidir") == ("prev", "out_first", 1, True)
+    assert plan(2, 4, "interleave:4") == ("own", "out_first", 4, False)
+    assert plan(3, 4, "interleave:4") == ("prev", "in_first", 4, False)
+    assert plan(1, 1, "stagger") == ("own", "out_first", 1, False)        # a single rank has nobody to stagger with
+    with pytest.raises(ValueError):
+        plan(0, 2, "nonsense")
+    assert set(bench.MULTI_GPU_VARIANTS) <= set(bench.VARIANT_TEXT)
