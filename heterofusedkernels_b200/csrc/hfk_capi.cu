@@ -419,7 +419,11 @@ static int swap_staged_impl(const hfk_swap_desc *d, const void *slots_host, void
                   (long long)slot_at(i), (long long)i);
   const int64_t per_round = (int64_t)(staging_bytes / (size_t)slot_bytes);
   const size_t id_width = d->ids_are_int64 ? 8 : 4;
-  if (ctas <= 0) ctas = sm_count();  // the packing kernel is HBM to HBM: spread it over the device
+  // The packing kernel is HBM to HBM.  A large call spreads it over the device (one CTA per SM, the
+  // gather's ring); a small one (a layer-wise swap next to running compute) takes the small ring whose
+  // CTAs share SMs with a compute kernel's instead of waiting for SMs to drain.
+  const bool small_pack = d->n_blocks * slot_bytes < kAutoBulkMinBytes;
+  if (ctas <= 0) ctas = small_pack ? kDefaultSwapCtasBulkSmall : sm_count();
   int n_lanes = g_staged_lanes.load() > 0 ? g_staged_lanes.load() : kDefaultStagedLanes;
   if (n_lanes > kMaxLanes) n_lanes = kMaxLanes;
   CopyLanes *lanes = nullptr;
@@ -439,19 +443,21 @@ static int swap_staged_impl(const hfk_swap_desc *d, const void *slots_host, void
     k.host_slot_stride = slot_bytes;
     k.num_host_slots = n;
     const SwapArgs a = to_args(&k);
-    const size_t tables = swap_tables_bytes(swap_id_tile(n), d->layers);
-    const BulkPlan p = plan_bulk(d->block_bytes, tables, kGatherStageBytes, kGatherStages, kGatherLag);
+    const int pack_tile = swap_id_tile(n, small_pack ? kSwapSmallIdTile : kSwapIdTile);
+    const size_t tables = swap_tables_bytes(pack_tile, d->layers);
+    const BulkPlan p = small_pack ? plan_bulk(d->block_bytes, tables, kSwapSmallStageBytes, kSwapSmallStages, kSwapLag)
+                                  : plan_bulk(d->block_bytes, tables, kGatherStageBytes, kGatherStages, kGatherLag);
     auto pack = [&](bool to_staging) -> cudaError_t {
       return launch_by_lag(p.lag, [&](auto lag) {
         cudaError_t err;
         if (to_staging) {
           auto kern = kv_swap_bulk_kernel<true, decltype(lag)::value>;
           if ((err = allow_smem(kern, p.smem)) != cudaSuccess) return err;
-          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, swap_id_tile(n));
+          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, pack_tile);
         } else {
           auto kern = kv_swap_bulk_kernel<false, decltype(lag)::value>;
           if ((err = allow_smem(kern, p.smem)) != cudaSuccess) return err;
-          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, swap_id_tile(n));
+          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, pack_tile);
         }
         return cudaGetLastError();
       });

@@ -354,3 +354,33 @@ def test_registry_is_safe_under_concurrent_registration_and_lookup(registry):
     for t in threads:
         t.join()
     assert errors == [] and lib.hfk_registry_count() == 0
+
+
+def test_accepted_host_strides_never_let_two_chunks_share_a_byte(hfk):
+    """Property: whenever the swap validation accepts a (slot, layer, K|V) stride triple, a brute-force
+    walk over every chunk finds no two chunks that overlap.  (The check is a sufficient condition — nested
+    strides — so some exotic non-overlapping layouts are refused; none that overlaps is accepted.)"""
+    import itertools
+    import random
+
+    rng = random.Random(11)
+    accepted = refused_but_fine = 0
+    for _ in range(600):
+        bb = rng.choice([16, 32, 48, 64])
+        layers, slots = rng.randint(1, 3), rng.randint(1, 4)
+        strides = [rng.choice([0, 16, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024]) for _ in range(3)]
+        # n_blocks = 0: the call validates everything and returns before it would launch anything
+        d, _keep = _swap_desc(hfk, block_bytes=bb, device_block_stride=bb, layers=layers, num_host_slots=slots,
+                              host_slot_stride=strides[0], host_layer_stride=strides[1], host_kv_stride=strides[2],
+                              n_blocks=0)
+        rc = hfk.lib().hfk_swap_out(C.byref(d), hfk.MOVER_AUTO, 0, None)
+        starts = [s * strides[0] + l * strides[1] + kv * strides[2]
+                  for s, l, kv in itertools.product(range(slots), range(layers), range(2))]
+        overlap = any(abs(a - b) < bb for a, b in itertools.combinations(starts, 2))
+        if rc == hfk.HFK_ERR_INVALID_ARG:
+            refused_but_fine += not overlap
+            continue
+        assert rc == hfk.HFK_OK, rc
+        assert not overlap, (bb, layers, slots, strides)
+        accepted += 1
+    assert accepted > 20        # the generator does produce valid layouts
