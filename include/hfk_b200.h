@@ -297,17 +297,22 @@ int hfk_swap_copy_engine(const hfk_swap_desc *desc_with_host_arrays, int to_host
 /* Staged swap through the copy engine.  Kernel-issued PCIe traffic moves in 128-byte
  * transactions and tops out near 92 % of what cudaMemcpyAsync reaches with 256-byte ones, so
  * this mover lets the copy engine cross the link: a short kernel packs the listed device
- * chunks into `staging` (HBM to HBM, slot-contiguous) and one cudaMemcpyAsync per host slot
- * moves [layers][K|V][block_bytes] at once (swap-in: the copies first, then the kernel
- * unpacks).  It is the multi-block form of the reference's staged transfer
+ * chunks into `staging` (HBM to HBM, slot-contiguous) and one cudaMemcpyAsync per RUN of
+ * consecutive host slots (cut at 64 MiB) moves [slots][layers][K|V][block_bytes] at once
+ * (swap-in: the copies first, then the kernel unpacks).  It pays off when the copies are
+ * 8 MiB or larger, i.e. when the slots of a call come in runs.  It is the multi-block form of
+ * the reference's staged transfer
  * (pcieThrough/csrc/host/multi_layer_block_transfer_torch.cpp:82-106).
  *
  * desc: as for hfk_swap_out, except that desc->host_slot_ids is not used and the pool must
  * be slot-contiguous (host_kv_stride == block_bytes, host_layer_stride == 2*block_bytes).
  * host_slot_ids_host: HOST array of desc->n_blocks ids (same width as the device ids);
  * host_pool_host: HOST address of the pinned pool; staging: device buffer of staging_bytes
- * >= one slot (layers*2*block_bytes); larger buffers mean fewer rounds.  Everything is
- * enqueued on `stream`; nothing is allocated. */
+ * >= one slot (layers*2*block_bytes); larger buffers mean fewer rounds.  With one copy lane
+ * (the default) everything is enqueued on `stream`; with more (hfk_set_staged_copy_lanes) the
+ * copies run on internal streams that fork from `stream` and join it again.  A one-layer view
+ * of a layer-major pool (layers == 1, any layer stride) counts as slot-contiguous.  Nothing is
+ * allocated per call. */
 int hfk_swap_staged(const hfk_swap_desc *desc, const void *host_slot_ids_host, void *host_pool_host,
                     void *staging, size_t staging_bytes, int to_host, int ctas, hfk_stream_t stream);
 
