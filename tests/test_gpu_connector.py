@@ -204,3 +204,51 @@ def test_connector_migrates_blocks_between_two_caches(ops, cuda_device):
         for d, c in zip(far.k_caches + far.v_caches, far_k + far_v):
             assert torch.equal(u8(d.cpu()), u8(c))
         torch.cuda.set_device(cuda_device)
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_sequence_of_connector_operations_matches_a_cpu_model(ops, cuda_device, seed):
+    """A seeded random run of what a KV-offload connector does — swap blocks out to slots the free list
+    hands out, bring some back into other blocks and release their slots, copy blocks inside the cache,
+    gather sequences — mirrored step by step on CPU tensors with the oracle; caches, pool and gathered
+    sequences must agree byte for byte at the end, and the free list must account for every slot."""
+    import random
+
+    rng = random.Random(seed)
+    layers, blocks, bs, heads, hd, slots = 3, 96, 8, 2, 32, 80
+    cache, cpu_k, cpu_v = _filled_cache(cuda_device, layers, blocks, bs, heads, hd, torch.float16, slots, seed=100 + seed)
+    cache.host_pool.view(torch.uint8).fill_(0x11)
+    ref_pool = cache.host_pool.clone()
+    held = []                                    # (slots tensor) of swapped-out block groups still on the host
+    for step in range(40):
+        op = rng.choice(["out", "out", "in", "copy", "gather"])
+        if op == "out" and cache.slot_pool.free_count >= 12:
+            n = rng.randint(1, 12)
+            ids = torch.tensor(rng.sample(range(blocks), n))
+            mover = rng.choice([None, 1, 2, "staged", "hybrid:0.5"])
+            got = cache.swap_out(ids, mover=mover)                      # slots from the free list
+            o.swap_out(cpu_k, cpu_v, ref_pool, ids, got)
+            held.append(got)
+        elif op == "in" and held:
+            got = held.pop(rng.randrange(len(held)))
+            ids = torch.tensor(rng.sample(range(blocks), got.numel()))
+            cache.swap_in(ids, got, mover=rng.choice([None, 1, 2, "staged", "hybrid:0.3"]), release=True)
+            o.swap_in(cpu_k, cpu_v, ref_pool, ids, got)
+        elif op == "copy":
+            pick = rng.sample(range(blocks), 2 * rng.randint(1, 10))
+            src, dst = torch.tensor(pick[:len(pick) // 2]), torch.tensor(pick[len(pick) // 2:])
+            cache.migrate_to(cache, src, dst)
+            o.migrate_blocks(cpu_k, cpu_v, cpu_k, cpu_v, src, dst)
+        elif op == "gather":
+            lens = [rng.randint(0, 5 * bs) for _ in range(rng.randint(1, 5))]
+            lens[0] = max(lens[0], 1)
+            tables = o.block_tables_for(lens, bs, blocks, seed=step)
+            k_out, v_out = cache.paged_gather(tables, torch.tensor(lens))
+            ko, vo = o.paged_gather(cpu_k, cpu_v, tables, torch.tensor(lens), bs)
+            assert torch.equal(u8(k_out.cpu()), u8(ko)) and torch.equal(u8(v_out.cpu()), u8(vo)), f"step {step}"
+    torch.cuda.synchronize()
+    assert torch.equal(u8(cache.host_pool), u8(ref_pool))
+    for d, c in zip(cache.k_caches + cache.v_caches, cpu_k + cpu_v):
+        assert torch.equal(u8(d.cpu()), u8(c))
+    assert cache.slot_pool.free_count == slots - sum(h.numel() for h in held)
+    assert cache.status() == 0
