@@ -311,6 +311,8 @@ class SwapBench:
       sequential  swap-out then swap-in of the same slots, one stream (N = 1 default)
       stagger     even ranks as sequential; odd ranks swap-in (prev) first, then swap-out
       bidir       swap-out and swap-in (prev) concurrently on two streams
+      bidir_paced the same with the swap-out's stores paced (PagedKVCache.BIDIR_OUT_PACE_GBS), which
+                  keeps the swap-in's read requests from being crowded out of the upstream lanes
       interleave:k  the step's lists cut into k parts, out/in parts alternating on one stream
                     (odd ranks: in (prev) first)
     """
@@ -338,13 +340,17 @@ class SwapBench:
         self.dev_sets = [tuple(t.to(cache.device) for t in s) for s in self.sets]
         self.pin_sets = [tuple(t.pin_memory() for t in s) for s in self.sets]
         self.side = [torch.cuda.Stream(cache.device), torch.cuda.Stream(cache.device)]
+        self.pace = None           # GB/s of the swap-outs of the running variant (bidir_paced)
         self.launches = 0          # swap calls issued so far
         self.launches_timed = 0    # ... of which inside the last run's timed region
 
     # one call each way; ids: device tensors (value leg) or pinned host tensors (e2e leg)
     def _out(self, ids, slots, slots_cpu):
         self.launches += 1
-        if isinstance(self.mover, str) and self.mover.startswith("hybrid"):
+        if self.pace:
+            self.cache.swap_out(ids, slots, aiv=self.aiv, mover=None if isinstance(self.mover, str) else self.mover,
+                                pace_gbs=self.pace)
+        elif isinstance(self.mover, str) and self.mover.startswith("hybrid"):
             self.cache.swap_out(ids, slots_cpu, aiv=self.aiv, mover=self.mover)
         elif self.mover == "staged":
             self.cache.swap_out_staged(ids, slots_cpu, staging_bytes=self.staging_bytes, aiv=self.aiv)
@@ -372,7 +378,7 @@ class SwapBench:
             return "own", "out_first", 1, False
         if variant == "stagger":
             return ("prev", "in_first", 1, False) if odd else ("own", "out_first", 1, False)
-        if variant == "bidir":
+        if variant in ("bidir", "bidir_paced"):
             return "prev", "out_first", 1, True
         if variant.startswith("interleave:"):
             k = max(1, int(variant.split(":")[1]))
@@ -384,6 +390,7 @@ class SwapBench:
         verification of the last step."""
         cache, ctx = self.cache, self.ctx
         src_mode, order, parts, two = self.plan(variant)
+        self.pace = type(cache).BIDIR_OUT_PACE_GBS if variant == "bidir_paced" else None
         use = self.pin_sets if e2e else self.dev_sets
         main = torch.cuda.current_stream(cache.device)
         t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -697,8 +704,9 @@ class OverlapBench:
                                   host_raw=host_raw, pool_layout=pool_layout)
         fill_random_bytes(self.cache._k_store, 1)
         fill_random_bytes(self.cache._v_store, 2)
-        self.pf = LayerwisePrefetcher(self.cache)                       # shipped default: one side stream
-        self.pf_two = LayerwisePrefetcher(self.cache, one_stream=False)
+        self.pf = LayerwisePrefetcher(self.cache)       # shipped default: two side streams, paced swap-out
+        self.pf_one = LayerwisePrefetcher(self.cache, one_stream=True)
+        self.pf_unpaced = LayerwisePrefetcher(self.cache, evict_pace_gbs=0)
         self.a = torch.randn(8192, 3584, device=device, dtype=torch.bfloat16)
         self.b = torch.randn(3584, 18944, device=device, dtype=torch.bfloat16)
         self.c = torch.empty(8192, 18944, device=device, dtype=torch.bfloat16)
@@ -750,10 +758,14 @@ class OverlapBench:
         "vector@<threads>x<loads in flight>[+pad<KiB of unused shared memory>]", "bulk" or "bulk@<stage bytes>x<stages>[+lag<k>]", "staged"
         (packing kernel + copy-engine transfers) or "copy_engine" (one copy per chunk)."""
         pkg, cache, L = self.pkg, self.cache, self.L
-        two = bool(kind) and kind.endswith("+2streams")
-        pf = self.pf_two if two else self.pf
-        if two:
-            kind = kind[:-len("+2streams")] or None
+        pace = None
+        if kind and "+pace" in kind:       # "...+pace40": the evict's stores paced to 40 GB/s
+            kind, p_txt = kind.rsplit("+pace", 1)
+            pace, kind = float(p_txt), (kind or None)
+        pf = self.pf
+        for suffix, which in (("+1stream", self.pf_one), ("+unpaced", self.pf_unpaced)):
+            if kind and kind.endswith(suffix):
+                pf, kind = which, (kind[:-len(suffix)] or None)
         lib = pkg.capi.lib()
         base_kind = (kind or "").split("@")[0].split("+")[0]
         mv = {"": None, "vector": pkg.capi.MOVER_VECTOR, "bulk": pkg.capi.MOVER_BULK, "staged": "staged",
@@ -812,7 +824,8 @@ class OverlapBench:
                         if markers:
                             lib.hfk_debug_stamp_marker(pf.out_stream.cuda_stream)
                         a.record()
-                    pf.evict(layers, out_ids, out_slots, aiv=ctas, mover=mv, after=False, host_slot_ids_cpu=out_slots_cpu)
+                    pf.evict(layers, out_ids, out_slots, aiv=ctas, mover=mv, after=False, host_slot_ids_cpu=out_slots_cpu,
+                             pace_gbs=pace)
                     with torch.cuda.stream(pf.out_stream):
                         b.record()
                     ev_out.append((a, b, len(layers)))
@@ -870,7 +883,7 @@ class OverlapBench:
         med_main = statistics.median(r["main_ms"] for r in runs)
         ver = self.verify(group)
         return {"mover": kind or "default", "ctas_per_direction": ctas or "default", "layers_per_launch": group,
-                "side_streams": 2 if (kind or "").endswith("+2streams") else 1, "pool_layout": self.pool_layout, "slots": "runs" if self.slot_runs else "random",
+                "side_streams": 1 if "+1stream" in (kind or "") else 2, "pool_layout": self.pool_layout, "slots": "runs" if self.slot_runs else "random",
                 "gemm_ms_alone": t_a, "gemm_ms_overlapped": med_main,
                 "gemm_slowdown_pct": 100.0 * (med_main / t_a - 1.0),
                 "gemm_tflops_alone": self.L * self.flops / (t_a * 1e-3) / 1e12,
@@ -922,15 +935,24 @@ def overlap_summary(ob: OverlapBench, reps: int, group: int) -> dict:
     sampler = ClockSampler(ob.device.index or 0)
     ob.warm(1.5)
     m = ob.measure(None, None, group, reps)
+    one = ob.measure("+1stream", None, group, max(2, reps // 2))
     clocks = sampler.stop()
     status = ob.cache.status()
     return {"workload": "qwen2_7b_fp8_prefetch",
-            "mover": "LayerwisePrefetcher defaults (bulk mover, 2 KiB x 4 ring, 64 CTAs, one side stream)",
+            "mover": "LayerwisePrefetcher defaults (bulk mover, 2 KiB x 4 ring, 64 CTAs; two side streams, "
+                     "swap-out paced to 40 GB/s)",
             "layers_per_launch": group, "gemm_slowdown_pct": m["gemm_slowdown_pct"], "swap_in_gbs": m["swap_in_gbs"],
-            "swap_out_gbs": m["swap_out_gbs"], "swap_in_gbs_no_gemm": m["swap_in_gbs_no_gemm"],
-            "swap_out_gbs_no_gemm": m["swap_out_gbs_no_gemm"], "gemm_tflops": m["gemm_tflops_alone"],
+            "swap_out_gbs": m["swap_out_gbs"], "both_directions_gbs": m["both_directions_gbs"],
+            "swap_in_gbs_no_gemm": m["swap_in_gbs_no_gemm"], "swap_out_gbs_no_gemm": m["swap_out_gbs_no_gemm"],
+            "one_stream_swap_in_gbs": one["swap_in_gbs"], "one_stream_swap_out_gbs": one["swap_out_gbs"],
+            "one_stream_both_directions_gbs": one["both_directions_gbs"],
+            "one_stream_gemm_slowdown_pct": one["gemm_slowdown_pct"],
+            "one_stream_swap_in_gbs_no_gemm": one["swap_in_gbs_no_gemm"],
+            "one_stream_swap_out_gbs_no_gemm": one["swap_out_gbs_no_gemm"],
+            "gemm_tflops": m["gemm_tflops_alone"],
             "gemm_ms_alone": m["gemm_ms_alone"], "gemm_ms_overlapped": m["gemm_ms_overlapped"],
-            "bytes_per_layer_per_direction": ob.layer_bytes, "verified": bool(m["verified"] and status == 0),
+            "bytes_per_layer_per_direction": ob.layer_bytes,
+            "verified": bool(m["verified"] and one["verified"] and status == 0),
             "bytes_checked": m["bytes_checked"], "status_word": status, "sm_mhz": clocks.get("sm_mhz"),
             "clock_reasons": ",".join(clocks.get("reasons", [])), "reps": reps}
 
@@ -944,16 +966,18 @@ def bench_overlap(g, device, args, pkg) -> dict:
     reps = args.overlap_reps
     variants = []
     table = [(None, None, 1), (None, None, 2), (None, None, 4), (None, None, 8),
-             ("+2streams", None, 1), ("+2streams", None, 4),
-             ("bulk", 32, 4), ("bulk", 128, 4), ("bulk@2048x8", 32, 4), ("bulk@4096x4", 32, 4), ("bulk@16384x8", 8, 8),
-             ("vector", 16, 4), ("vector@256x8", 32, 4), ("vector@128x8", 64, 4), ("vector+2streams", 16, 4)]
+             ("+pace44", None, 4), ("+pace42", None, 4), ("+pace41", None, 4), ("+pace38", None, 4), ("+unpaced", None, 4),
+             ("+1stream", None, 1), ("+1stream", None, 4), ("+1stream", None, 8),
+             ("bulk+1stream", 32, 4), ("bulk@4096x4+1stream", 32, 4), ("bulk@16384x8+1stream", 8, 8),
+             ("vector+1stream", 16, 4), ("vector@256x8+1stream", 32, 4), ("vector+unpaced", 16, 4)]
     if args.overlap_quick:
         table = table[:2]
     for kind, ctas, group in table:
         variants.append(ob.measure(kind, ctas, group, reps))
     stamps = []
     for kind, ctas in (() if args.overlap_quick else
-                       ((None, None), ("bulk@4096x4", 32), ("bulk@16384x8", 4), ("vector", 16), ("vector@256x8", 32))):
+                       (("+1stream", None), ("bulk@4096x4+1stream", 32), ("bulk@16384x8+1stream", 4),
+                        ("vector+1stream", 16), ("vector@256x8+1stream", 32))):
         for direction in ("in", "out"):
             stamps.append(ob.stamps(kind, ctas, 1, direction))
     status = ob.cache.status()
@@ -962,7 +986,7 @@ def bench_overlap(g, device, args, pkg) -> dict:
     # the same pipeline on a layer-major pool with slots handed out as runs: one copy-engine transfer per
     # layer and direction (staged), next to the kernel movers on the same layout
     ob = OverlapBench(g, device, pkg, pool_layout="layer_major", slot_runs=True)
-    for kind, ctas, group in (("staged", None, 4), ("staged@2048x4", 64, 4), (None, None, 4)):
+    for kind, ctas, group in (("staged+1stream", None, 4), ("staged@2048x4+1stream", 64, 4), (None, None, 4)):
         variants.append(ob.measure(kind, ctas, group, reps))
     clocks = sampler.stop()
     status |= ob.cache.status()
@@ -1322,7 +1346,11 @@ def main() -> None:
 
     # ---- optional extra variants on the same state ---------------------------------------------
     extra = {}
-    for var in [v for v in args.variants.split(",") if v]:
+    for var_full in [v for v in args.variants.split(",") if v]:
+        var = var_full
+        if "+pace" in var:     # e.g. bidir+pace44: swap-outs of the bulk mover paced to 44 GB/s
+            var, pace = var.split("+pace")
+            pkg.capi.check(lib.hfk_set_swap_out_pace(int(float(pace) * 1000)), "hfk_set_swap_out_pace")
         if var.startswith("staged"):   # "staged" or "staged:<lanes>"
             lanes = int(var.split(":")[1]) if ":" in var else 0
             lib.hfk_set_staged_copy_lanes(lanes)
@@ -1340,8 +1368,9 @@ def main() -> None:
             sb.mover = mover
         else:
             r = timed_leg(sb, var, args.steps, args.warmup, e2e=False)
+        lib.hfk_set_swap_out_pace(0)
         per = ctx.gather_floats([r["out_gbs"], r["in_gbs"]])
-        extra[var] = {"value": r["value"], "ms_per_step": r["ms_per_step"], "verified": r["all_verified"],
+        extra[var_full] = {"value": r["value"], "ms_per_step": r["ms_per_step"], "verified": r["all_verified"],
                       "swap_out_GBps_per_rank": [round(p[0], 2) for p in per],
                       "swap_in_GBps_per_rank": [round(p[1], 2) for p in per], "plan_rank0": r["plan"]}
     # ---- the same step with the slots a fresh free list hands out (one run per step), public API ----
@@ -1461,6 +1490,12 @@ def main() -> None:
     if overlap is not None:
         roofline.update({"overlap_gemm_slowdown_pct": overlap["gemm_slowdown_pct"],
                          "overlap_swap_in_gbs": overlap["swap_in_gbs"], "overlap_swap_out_gbs": overlap["swap_out_gbs"],
+                         "overlap_both_directions_gbs": overlap["both_directions_gbs"],
+                         "overlap_one_stream_swap_in_gbs": overlap["one_stream_swap_in_gbs"],
+                         "overlap_one_stream_swap_out_gbs": overlap["one_stream_swap_out_gbs"],
+                         "overlap_one_stream_gemm_slowdown_pct": overlap["one_stream_gemm_slowdown_pct"],
+                         "overlap_one_stream_swap_in_gbs_no_gemm": overlap["one_stream_swap_in_gbs_no_gemm"],
+                         "overlap_one_stream_swap_out_gbs_no_gemm": overlap["one_stream_swap_out_gbs_no_gemm"],
                          "overlap_swap_in_gbs_no_gemm": overlap["swap_in_gbs_no_gemm"],
                          "overlap_swap_out_gbs_no_gemm": overlap["swap_out_gbs_no_gemm"],
                          "overlap_gemm_tflops": overlap["gemm_tflops"], "overlap_verified": overlap["verified"]})
@@ -1508,13 +1543,15 @@ def main() -> None:
 # Issue orders of a step that are timed when several ranks share the host (see SwapBench): which one
 # is faster depends on the host — how far its device->host path sags with several links writing at
 # once — so the default run measures them and reports the faster.
-MULTI_GPU_VARIANTS = ("bidir", "stagger")
+MULTI_GPU_VARIANTS = ("bidir_paced", "stagger")
 # Layers per launch of the prefetch pipeline in the default line's `overlap` run.
 DEFAULT_PREFETCH_GROUP = 4
 VARIANT_TEXT = {
     "sequential": "swap-out then swap-in of the same slots, one stream",
     "stagger": "odd ranks swap-in (the previous step's slots) first, even ranks swap-out first",
     "bidir": "swap-out and swap-in (the previous step's slots) concurrently on two streams per rank",
+    "bidir_paced": "swap-out (stores paced to 40 GB/s) and swap-in (the previous step's slots) concurrently on two "
+                   "streams per rank",
     "interleave": "each step cut into k parts, swap-out and swap-in parts alternating; odd ranks start with swap-in",
 }
 

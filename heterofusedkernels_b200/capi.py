@@ -129,6 +129,7 @@ PROTOTYPES = {
     "hfk_set_bulk_lag": (C.c_int, [C.c_int]),
     "hfk_set_vector_geometry": (C.c_int, [C.c_int, C.c_int]),
     "hfk_set_vector_smem_pad": (C.c_int, [C.c_int]),
+    "hfk_set_swap_out_pace": (C.c_int, [C.c_int]),
     "hfk_set_gather_tuning": (C.c_int, [C.c_int, C.c_int]),
     "hfk_set_staged_copy_lanes": (C.c_int, [C.c_int]),
     "hfk_debug_set_stamps": (C.c_int, [C.c_void_p, C.c_size_t]),
@@ -158,6 +159,7 @@ PROTOTYPES = {
         C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int,
                   C.c_void_p]),
     "hfk_swap_out": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_int, C.c_void_p]),
+    "hfk_swap_out_paced": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "hfk_swap_in": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_int, C.c_void_p]),
     "hfk_swap_copy_engine": (C.c_int, [C.POINTER(SwapDesc), C.c_int, C.c_void_p]),
     "hfk_swap_staged": (C.c_int, [C.POINTER(SwapDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int,

@@ -131,6 +131,9 @@ class PagedKVCache:
     STAGED_MIN_RUN = 4
     HYBRID_FRACTION = 0.4            # share of a "hybrid" swap that goes through the copy engine
     HYBRID_MIN_BYTES = 128 << 20
+    # Pace of a swap-out that runs at the same time as a swap-in on the same link (1.07 GB each way on
+    # Gen5 x16: unpaced 42.9 GB/s out with 34.5 in; paced to 40: 40.0 out with 42.0 in).
+    BIDIR_OUT_PACE_GBS = 40.0
 
     def __init__(self, layers: int, num_blocks: int, block_size: int, kv_heads: int, head_dim: int,
                  dtype: torch.dtype, device: torch.device | str = "cuda", host_slots: int = 0,
@@ -230,15 +233,24 @@ class PagedKVCache:
         return ids if ids.device.type == "cpu" else ids.cpu()
 
     def swap_out(self, device_block_ids, host_slot_ids=None, aiv: Optional[int] = None,
-                 mover: MoverArg = None) -> torch.Tensor:
+                 mover: MoverArg = None, pace_gbs: Optional[float] = None) -> torch.Tensor:
         """host_pool[slot] <- cache[block], every layer, K and V, one call, current stream.
 
         Without ``host_slot_ids`` the slots come from the free list (``self.slot_pool``), as runs of
         consecutive slots where possible; the slots used are returned (give them back with
-        ``release`` once the blocks have been swapped in again or dropped)."""
+        ``release`` once the blocks have been swapped in again or dropped).
+
+        ``pace_gbs`` paces the stores of the (bulk) kernel to that many GB/s: for a swap-out that
+        crosses the link at the same time as a swap-in (``BIDIR_OUT_PACE_GBS`` is the measured
+        balance point); a paced swap-out always goes through the kernel."""
         n = len(device_block_ids)
         if host_slot_ids is None:
             host_slot_ids = self.slot_pool.alloc(n)
+        if pace_gbs:
+            torch.ops.pcie_through.swap_out(self.k_ptrs, self.v_ptrs, self.host_pool, self._ids(device_block_ids),
+                                            self._ids(host_slot_ids), self.num_blocks, None, aiv,
+                                            None if isinstance(mover, str) else mover, int(pace_gbs * 1000))
+            return host_slot_ids
         if mover is None:
             mover = self._pick_mover(host_slot_ids)
         if mover == "staged":
@@ -416,21 +428,24 @@ class LayerwisePrefetcher:
 
     Defaults: the library's mover for small launches — the bulk mover with a 2 KiB x 4 ring and 64
     single-warp CTAs, whose CTAs fit next to a GEMM's on an SM — four layers per launch (pass a range;
-    one layer per launch loses about 15 % to the launch itself), and ONE side stream for both
-    directions.  Measured next to a bf16 GEMM that fills the device (fp8 cache, 256 blocks per layer
-    and direction): 48.3 GB/s in and 49.5 out with the GEMM 1.8 % slower; alone 48.6 / 50.1.
+    one layer per launch loses about 15 % to the launch itself), and TWO side streams with the
+    swap-out's stores paced to ``EVICT_PACE_GBS``.  Measured next to a bf16 GEMM that fills the device
+    (fp8 cache, 256 blocks per layer and direction, four layers per launch): 38.8 GB/s in and 38.9 out
+    AT THE SAME TIME (76.8 together) with the GEMM 0.7 % slower.  Unpaced, the swap-out crowds the
+    swap-in's read requests out of the upstream lanes: 28.6 in / 43.6 out (56.8 together).  One side
+    stream (``one_stream=True``) runs the directions one after the other, each at the link's
+    one-direction rate: 48.3 in, then 46.9 out (47.3 for the pair), GEMM 4 % slower.
     """
     DEFAULT_AIV = None      # library default of the mover
     DEFAULT_MOVER = None    # HFK_MOVER_AUTO
     RECOMMENDED_LAYERS_PER_LAUNCH = 4
+    EVICT_PACE_GBS = PagedKVCache.BIDIR_OUT_PACE_GBS
 
-    def __init__(self, cache: PagedKVCache, one_stream: bool = True):
-        """``one_stream=True`` (default) issues swap-ins and swap-outs on ONE side stream, so the two
-        directions never cross the link at the same time and each runs at the full one-direction rate —
-        what the swap-in, which the next layer waits for, needs.  With two streams the pair moves more
-        bytes per second in total (54-58 GB/s against 49 next to a GEMM), but the swap-in falls to
-        27-30 GB/s while the swap-out keeps 45-48: the upstream lanes carry the swap-out's writes and the
-        swap-in's read requests."""
+    def __init__(self, cache: PagedKVCache, one_stream: bool = False, evict_pace_gbs: Optional[float] = None):
+        """``one_stream=True`` issues swap-ins and swap-outs on ONE side stream, so the two directions never
+        cross the link at the same time.  ``evict_pace_gbs``: pace of the swap-outs when there are two side
+        streams (``None`` = ``EVICT_PACE_GBS``, 0 = unpaced); with one stream swap-outs are never paced."""
+        self.evict_pace_gbs = 0.0 if one_stream else (self.EVICT_PACE_GBS if evict_pace_gbs is None else evict_pace_gbs)
         self.cache = cache
         self.in_stream = torch.cuda.Stream(device=cache.device, priority=-1)
         self.out_stream = self.in_stream if one_stream else torch.cuda.Stream(device=cache.device, priority=-1)
@@ -505,11 +520,13 @@ class LayerwisePrefetcher:
 
     def evict(self, layer: LayerArg, device_block_ids: torch.Tensor, host_slot_ids: torch.Tensor,
               aiv: Optional[int] = None, mover: MoverArg = None, after=None,
-              host_slot_ids_cpu: Optional[torch.Tensor] = None) -> torch.cuda.Event:
+              host_slot_ids_cpu: Optional[torch.Tensor] = None, pace_gbs: Optional[float] = None) -> torch.cuda.Event:
         """Swap-out of the listed blocks of ``layer`` (an index or a range) on the swap-out stream.
-        Returns the event to wait for before the blocks are reused."""
+        Returns the event to wait for before the blocks are reused.  ``pace_gbs`` paces the kernel's
+        stores (two side streams: keeps the swap-in of the other stream from starving)."""
         first, last = self._span(layer)
         k_ptrs, v_ptrs, pool = self._view(first, last)
+        pace = self.evict_pace_gbs if pace_gbs is None else pace_gbs
         self._order(self.out_stream, after)
         with torch.cuda.stream(self.out_stream):
             if mover == "staged":
@@ -519,7 +536,8 @@ class LayerwisePrefetcher:
                 torch.ops.pcie_through.swap_out(k_ptrs, v_ptrs, pool, device_block_ids, host_slot_ids,
                                                 self.cache.num_blocks, None,
                                                 self.DEFAULT_AIV if aiv is None else aiv,
-                                                self.DEFAULT_MOVER if mover is None else mover)
+                                                self.DEFAULT_MOVER if mover is None else mover,
+                                                int(pace * 1000) if pace and mover != _pkg.capi.MOVER_VECTOR else None)
             for l in range(first, last):
                 self.evicted[l].record()
         device_block_ids.record_stream(self.out_stream)

@@ -229,10 +229,17 @@ struct PumpSmem {
 // into this CTA's shared memory when it exits, and the caller must stop issuing work.  After
 // a timeout the destination of the whole call is undefined.
 constexpr uint64_t kDrainLimitNs = 100000000ull;  // 0.1 s per stage that still has a load in flight
+//
+// pace_ns_per_kib > 0 paces the STORES of this CTA: the k-th KiB is not stored before
+// t_start + k * pace_ns_per_kib (on %globaltimer).  A swap-out paced a little below the link's
+// write rate leaves room on the upstream lanes for the read requests of a swap-in that runs at
+// the same time.  The pacing wait ends at a computed time and is bounded in iterations as well.
+constexpr int kPaceSpinLimit = 1 << 20;
 template <int kPumpLag, typename MakeDesc>
 __device__ __forceinline__ bool run_pump(PumpSmem *ps, unsigned char *stages, int stage_bytes,
                                          int n_stages, int64_t total, uint32_t &seq,
-                                         MakeDesc make_desc, int hints = 0) {
+                                         MakeDesc make_desc, int hints = 0, float pace_ns_per_kib = 0.f,
+                                         uint64_t pace_t0 = 0, uint64_t *paced_bytes = nullptr) {
   // hints: bit 0 = loads carry an L2 evict-first policy, bit 1 = stores do
   const int lane = threadIdx.x & 31;
   const uint64_t policy = hints ? make_evict_first_policy() : 0;
@@ -281,6 +288,12 @@ __device__ __forceinline__ bool run_pump(PumpSmem *ps, unsigned char *stages, in
       if (lane == 0) {
         ok = mbar_wait_bounded(&ps->full[slot], parity);
         if (ok) {
+          if (pace_ns_per_kib > 0.f) {
+            const uint64_t due = pace_t0 + (uint64_t)((float)(*paced_bytes >> 10) * pace_ns_per_kib);
+            for (int spin = 0; spin < kPaceSpinLimit && global_timer_ns() < due; ++spin) {
+            }
+            *paced_bytes += d.bytes;
+          }
           fence_async_proxy();
           if (hints & 2)
             bulk_store_hint(d.dst, stages + (size_t)slot * stage_bytes, d.bytes, policy);

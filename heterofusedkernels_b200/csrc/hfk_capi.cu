@@ -57,6 +57,7 @@ __global__ void status_exchange_kernel(unsigned int slot) {
 std::atomic<int> g_stage_bytes{0}, g_n_stages{0}, g_bulk_lag{0}, g_vec_threads{0}, g_vec_unroll{0};
 std::atomic<int> g_gather_hints{-1}, g_gather_blocked{-1};
 std::atomic<int> g_staged_lanes{0};
+std::atomic<int> g_swap_out_pace_mbs{0};  // pacing of bulk swap-outs in MB/s, 0 = unpaced (hfk_set_swap_out_pace)
 std::atomic<int> g_vec_smem_pad{0};  // extra dynamic shared memory of the vector swap kernels (see hfk_set_vector_smem_pad)
 
 // ---- copy lanes of the staged mover -------------------------------------------
@@ -227,7 +228,7 @@ static cudaError_t launch_swap_vector(const SwapArgs &a, int ctas, size_t smem, 
 }
 
 template <bool kToHost>
-static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t stream) {
+static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t stream, int pace_mbs_arg = 0) {
   int rc = validate_swap(d);
   if (rc != HFK_OK) return rc;
   if (d->n_blocks == 0) return HFK_OK;
@@ -265,11 +266,15 @@ static int swap_impl(const hfk_swap_desc *d, int mover, int ctas, cudaStream_t s
     if (ctas <= 0) ctas = small ? kDefaultSwapCtasBulkSmall : kDefaultSwapCtasBulk;
     const int64_t pieces = (d->block_bytes + p.stage_bytes - 1) / p.stage_bytes;
     if (ctas > items * pieces) ctas = (int)(items * pieces);
+    // pacing (swap-out only): every CTA moves an equal share, so its stores are spaced for rate / ctas
+    float pace_ns_per_kib = 0.f;
+    const int pace_mbs = pace_mbs_arg > 0 ? pace_mbs_arg : g_swap_out_pace_mbs.load();
+    if (kToHost && pace_mbs > 0) pace_ns_per_kib = 1024.0f * 1000.0f * (float)ctas / (float)pace_mbs;
     cudaError_t e = launch_by_lag(p.lag, [&](auto lag) {
       auto k = kv_swap_bulk_kernel<kToHost, decltype(lag)::value>;
       cudaError_t err = allow_smem(k, p.smem);
       if (err != cudaSuccess) return err;
-      k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, id_tile);
+      k<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, id_tile, pace_ns_per_kib);
       return cudaGetLastError();
     });
     if (e != cudaSuccess) return cuda_fail(e, "kv_swap_bulk_kernel launch");
@@ -453,11 +458,11 @@ static int swap_staged_impl(const hfk_swap_desc *d, const void *slots_host, void
         if (to_staging) {
           auto kern = kv_swap_bulk_kernel<true, decltype(lag)::value>;
           if ((err = allow_smem(kern, p.smem)) != cudaSuccess) return err;
-          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, pack_tile);
+          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, pack_tile, 0.f);
         } else {
           auto kern = kv_swap_bulk_kernel<false, decltype(lag)::value>;
           if ((err = allow_smem(kern, p.smem)) != cudaSuccess) return err;
-          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, pack_tile);
+          kern<<<ctas, 32, p.smem, stream>>>(a, p.stage_bytes, p.n_stages, pack_tile, 0.f);
         }
         return cudaGetLastError();
       });
@@ -771,6 +776,14 @@ int hfk_set_vector_geometry(int threads, int unroll) {
 int hfk_swap_out(const hfk_swap_desc *desc, int mover, int ctas, hfk_stream_t stream) {
   return swap_impl<true>(desc, mover, ctas, stream);
 }
+int hfk_swap_out_paced(const hfk_swap_desc *desc, int mover, int ctas, int megabytes_per_second,
+                       hfk_stream_t stream) {
+  if (megabytes_per_second < 0 || megabytes_per_second > 1000000)
+    return fail(HFK_ERR_INVALID_ARG, "swap_out_paced: pace 0 (unpaced) .. 1000000 MB/s");
+  if (megabytes_per_second > 0 && mover == HFK_MOVER_VECTOR)
+    return fail(HFK_ERR_UNSUPPORTED, "swap_out_paced: only the bulk mover can be paced");
+  return swap_impl<true>(desc, mover, ctas, stream, megabytes_per_second);
+}
 int hfk_swap_in(const hfk_swap_desc *desc, int mover, int ctas, hfk_stream_t stream) {
   return swap_impl<false>(desc, mover, ctas, stream);
 }
@@ -914,6 +927,13 @@ int hfk_enable_peer_access(int peer_device) {
     return HFK_OK;
   }
   if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceEnablePeerAccess");
+  return HFK_OK;
+}
+
+int hfk_set_swap_out_pace(int megabytes_per_second) {
+  if (megabytes_per_second < 0 || megabytes_per_second > 1000000)
+    return fail(HFK_ERR_INVALID_ARG, "swap-out pace: 0 (unpaced) .. 1000000 MB/s");
+  g_swap_out_pace_mbs = megabytes_per_second;
   return HFK_OK;
 }
 

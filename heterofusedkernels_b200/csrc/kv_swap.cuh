@@ -134,9 +134,11 @@ __global__ void __launch_bounds__(kThreads) kv_swap_vector_kernel(SwapArgs a, in
 // ---- mover 2: one warp per CTA pumping bulk copies -------------------------
 // Unit = one piece (<= stage_bytes) of one chunk.  Shared memory: stages, then
 // PumpSmem, then SwapTables, then the layer pointers.
+// pace_ns_per_kib: 0, or the pacing of this CTA's stores (see run_pump); used for swap-outs.
 template <bool kToHost, int kLag>
 __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_bytes,
-                                                          int n_stages, int id_tile) {
+                                                          int n_stages, int id_tile,
+                                                          float pace_ns_per_kib) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char *stages = smem_raw;
   PumpSmem *ps = reinterpret_cast<PumpSmem *>(smem_raw + (size_t)stage_bytes * n_stages);
@@ -154,6 +156,8 @@ __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_
   const int per_block = 2 * a.layers;
   const int pieces = (int)((a.block_bytes + stage_bytes - 1) / stage_bytes);
   uint32_t seq = 0;
+  const uint64_t pace_t0 = pace_ns_per_kib > 0.f ? global_timer_ns() : 0;
+  uint64_t paced_bytes = 0;
   for (int64_t tile0 = 0; tile0 < a.n_blocks; tile0 += id_tile) {
     const int tn = (int)min((int64_t)id_tile, a.n_blocks - tile0);
     __syncwarp();
@@ -182,7 +186,7 @@ __global__ void __launch_bounds__(32) kv_swap_bulk_kernel(SwapArgs a, int stage_
       d.src = kToHost ? dp : hp;
       d.dst = kToHost ? hp : dp;
       return d;
-    });
+    }, 0, pace_ns_per_kib, pace_t0, &paced_bytes);
     if (!ok) break;  // a wait ran out: the barriers are out of step, issue nothing more
   }
   stamp.end();

@@ -186,12 +186,15 @@ static int mover_from(const c10::optional<int64_t> &mover) {
 void swap_out(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs, const at::Tensor &hostPool,
               const at::Tensor &deviceBlockIds, const at::Tensor &hostSlotIds,
               int64_t numDeviceBlocks, c10::optional<int64_t> deviceBlockStride,
-              c10::optional<int64_t> aiv, c10::optional<int64_t> mover) {
+              c10::optional<int64_t> aiv, c10::optional<int64_t> mover, c10::optional<int64_t> paceMBs) {
   const int ctas = cores_from(aiv);
   const hfk_swap_desc d = swap_desc(kLayerPtrs, vLayerPtrs, hostPool, deviceBlockIds, hostSlotIds,
                                     numDeviceBlocks, deviceBlockStride, true, "swap_out");
   const c10::cuda::CUDAGuard guard(kLayerPtrs.device());
-  check_rc(hfk_swap_out(&d, mover_from(mover), ctas, at::cuda::getCurrentCUDAStream().stream()), "swap_out");
+  // paceMBs: stores paced to that many MB/s (for a swap-out that shares the link with a swap-in)
+  check_rc(hfk_swap_out_paced(&d, mover_from(mover), ctas, paceMBs.has_value() ? static_cast<int>(paceMBs.value()) : 0,
+                              at::cuda::getCurrentCUDAStream().stream()),
+           "swap_out");
 }
 
 void swap_in(const at::Tensor &kLayerPtrs, const at::Tensor &vLayerPtrs, const at::Tensor &hostPool,
@@ -432,7 +435,7 @@ TORCH_LIBRARY_FRAGMENT(pcie_through, m) {
   m.def("gather(Tensor gmEmbed, Tensor gmEmbedDst, Tensor gmIds, int? aiv=None) -> ()");
   m.def("multi_layer_block_transfer(Tensor deviceBlockCachePtrs, Tensor hostBlockCache, int? aiv=None) -> ()");
   m.def("fused_memcpy_multi_layer_block_transfer(Tensor deviceBlockCachePtrs, Tensor hostBlockCache, Tensor stagingBlockCache, int? aiv=None) -> ()");
-  m.def("swap_out(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None, int? mover=None) -> ()");
+  m.def("swap_out(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None, int? mover=None, int? paceMBs=None) -> ()");
   m.def("swap_in(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None, int? aiv=None, int? mover=None) -> ()");
   m.def("swap_out_copy_engine(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None) -> ()");
   m.def("swap_in_copy_engine(Tensor kLayerPtrs, Tensor vLayerPtrs, Tensor hostPool, Tensor deviceBlockIds, Tensor hostSlotIds, int numDeviceBlocks, int? deviceBlockStride=None) -> ()");

@@ -86,6 +86,9 @@ int hfk_set_bulk_geometry(int stage_bytes, int n_stages);
  * loads in flight); compiled values 1, 2, 3, 4, 6, 8; 0 restores the default. */
 int hfk_set_bulk_lag(int lag);
 int hfk_set_vector_geometry(int threads, int unroll);
+/* Process-wide default pace of the bulk mover's swap-outs in MB/s for calls that give none
+ * (hfk_swap_out, or hfk_swap_out_paced with 0); 0 = unpaced.  See hfk_swap_out_paced. */
+int hfk_set_swap_out_pace(int megabytes_per_second);
 /* Measurement knob: unused dynamic shared memory added to every CTA of the vector swap kernels
  * (multiple of 128, up to 200 KiB; 0 = none).  With enough of it a compute kernel's CTAs can no
  * longer share an SM with a swap CTA, which is how the cost of sharing is measured. */
@@ -280,6 +283,14 @@ typedef struct hfk_swap_desc {
  *   host chunk(host_slot_ids[i], l, kv) = device chunk(device_block_ids[i], l, kv)
  * one launch for all layers.  host slots must be distinct. */
 int hfk_swap_out(const hfk_swap_desc *desc, int mover, int ctas, hfk_stream_t stream);
+
+/* Swap-out whose stores are paced to about `megabytes_per_second` (1 MB = 1e6 bytes; 0 = unpaced, the
+ * same as hfk_swap_out; bulk mover only).  For a swap-out that shares the link with a swap-in: the
+ * upstream lanes carry the swap-out's write TLPs AND the swap-in's read requests, and an unpaced
+ * swap-out crowds the requests out (one B200 on Gen5 x16, 1.07 GB each way at once: 42.9 GB/s out with
+ * 34.5 in unpaced; 40.0 out with 42.0 in when paced to 40 000 MB/s). */
+int hfk_swap_out_paced(const hfk_swap_desc *desc, int mover, int ctas, int megabytes_per_second,
+                       hfk_stream_t stream);
 
 /* Swap-in: the inverse copy; device block ids must be distinct. */
 int hfk_swap_in(const hfk_swap_desc *desc, int mover, int ctas, hfk_stream_t stream);

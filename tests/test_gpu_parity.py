@@ -136,6 +136,28 @@ def test_swap_with_the_ring_of_large_launches_forced(hfk, cuda_device, ring, sha
         hfk.lib().hfk_set_bulk_geometry(0, 0)
 
 
+@pytest.mark.parametrize("pace_mbs", [500, 20000, 1000000])
+def test_paced_swap_out_moves_the_same_bytes(hfk, cuda_device, pace_mbs):
+    """hfk_swap_out_paced spaces the stores in time; the bytes are those of hfk_swap_out."""
+    case = SwapCase(hfk, cuda_device, 3, 40, (16, 2, 64), torch.bfloat16, 48, seed=17)
+    try:
+        ids, slots = o.distinct_ids(25, 40, 1), o.distinct_ids(25, 48, 2)
+        d = case.desc(ids.to(cuda_device), slots.to(cuda_device))
+        lib = hfk.lib()
+        for mover in (0, 2):
+            case.pool.tensor.view(torch.uint8).fill_(0xA5)
+            hfk.check(lib.hfk_swap_out_paced(C.byref(d), mover, 3, pace_mbs, stream_handle()), "paced swap-out")
+            torch.cuda.synchronize()
+            expect = case.cpu_pool.clone()
+            o.swap_out(case.cpu_k, case.cpu_v, expect, ids, slots)
+            assert same_bytes(case.pool_view, expect)
+        assert lib.hfk_swap_out_paced(C.byref(d), 1, 0, pace_mbs, stream_handle()) == hfk.HFK_ERR_UNSUPPORTED
+        assert lib.hfk_swap_out_paced(C.byref(d), 0, 0, -5, stream_handle()) == hfk.HFK_ERR_INVALID_ARG
+        assert hfk.device_status() == 0
+    finally:
+        case.close()
+
+
 def _swap_round_trip(hfk, cuda_device, mover, shape):
     layers, blocks, chunk, dtype, nslots, n, layout, pad, idt = shape
     case = SwapCase(hfk, cuda_device, layers, blocks, chunk, dtype, nslots, seed=11, pool_layout=layout,

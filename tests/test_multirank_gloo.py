@@ -109,6 +109,7 @@ def test_issue_orders_of_a_step_per_rank():
     assert plan(0, 2, "stagger") == ("own", "out_first", 1, False)
     assert plan(1, 2, "stagger") == ("prev", "in_first", 1, False)        # odd ranks swap in first
     assert plan(0, 8, "bidir") == plan(5, 8, "bidir") == ("prev", "out_first", 1, True)
+    assert plan(3, 4, "bidir_paced") == plan(0, 8, "bidir")                 # the same order; only the swap-out is paced
     assert plan(2, 4, "interleave:4") == ("own", "out_first", 4, False)
     assert plan(3, 4, "interleave:4") == ("prev", "in_first", 4, False)
     assert plan(1, 1, "stagger") == ("own", "out_first", 1, False)        # a single rank has nobody to stagger with
